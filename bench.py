@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of the ternary sparse product hot path on B200.
+
+Workload (the configuration the headline metric is quoted on): decode ternary SpMV, Llama-7B
+up-projection shape -- x [M=1, 4096] fp16 ~ N(0,1), W [4096, 11008] ternary with 75 % zeros and +-1
+equiprobable, per-tensor fp16 scale ~ U(0.01, 0.05), seeded synthetic data.
+
+One step = one decode token pushed through R distinct packed weights of that shape (R*bytes is several
+times the L2 capacity, so every launch streams its weight from HBM).  `value` is algorithmic GB/s
+(B_alg per launch / average launch time): B_alg = 2*nnz + 16*N*ceil(K/512) + e*M*(K+N) + 4 bytes, the
+bytes of the reference's own layout.  `e2e` is the same metric through the host-buffer C-ABI entry point
+(tllm_spmm_host): pinned host x -> device, kernel, y -> host, every call.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--rows M] [--sparsity S]
+
+With --impl reference the reference's own CPU GEMV kernels (compiled in place into oracle/_ref) are timed
+on the host cores for the same workload; that arm launches no GPU kernel.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+K_IN, N_OUT = 4096, 11008
+L2_BYTES = 126 * 1024 * 1024
+METRIC = "ternary_spmv_algorithmic_hbm_gbps"
+# DRAM bytes per launch of the decode kernel from an ncu capture of this workload
+# (dram__bytes_read.sum + dram__bytes_write.sum; see profiles/), or None when no capture has been taken.
+NCU_TRAFFIC_BYTES = None
+
+
+def make_weight(seed: int, K: int, N: int, sparsity: float) -> np.ndarray:
+    rng = np.random.default_rng(seed)
+    if abs(sparsity * 256 - round(sparsity * 256)) < 1e-9:
+        z = int(round(sparsity * 256))
+        half = (256 - z) // 2
+        r = rng.integers(0, 256, size=(K, N), dtype=np.uint8)
+        w = np.zeros((K, N), np.int8)
+        w[(r >= z) & (r < z + half)] = -1
+        w[r >= z + half] = 1
+        return w
+    r = rng.random((K, N), dtype=np.float32)
+    w = np.zeros((K, N), np.int8)
+    w[(r >= sparsity) & (r < (sparsity + 1) / 2)] = -1
+    w[r >= (sparsity + 1) / 2] = 1
+    return w
+
+
+def algorithmic_bytes(nnz: int, K: int, N: int, M: int, e: int) -> int:
+    return 2 * nnz + 16 * N * (-(-K // 512)) + e * M * (K + N) + 4
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
+        self._t = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._n = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._n = None
+
+    def _run(self):
+        n = self._n
+        names = {
+            getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
+                try:
+                    r = n.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    r = n.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self._n:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._t:
+            self._t.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------------
+# reference CPU arm
+# ------------------------------------------------------------------------------------------------------
+GEMV_CANDIDATES = [   # (group, kernel name, simd chunk of the format)
+    (64, "GEMV_CPU_FP32_rowMajor_TCSC_Merged_GroupMin_G64_AVX512_OpenMP", 0),
+    (128, "GEMV_CPU_FP32_rowMajor_TCSC_Merged_GroupMin_G128_CS16_AVX512_OpenMP", 16),
+    (32, "GEMV_CPU_FP32_rowMajor_TCSC_Merged_GroupMin_G32_AVX512_OpenMP", 0),
+    (64, "GEMV_CPU_FP32_rowMajor_TCSC_Merged_GroupMin_G64_AVX2_OpenMP", 0),
+]
+
+
+def cpu_reference_run(weights, x_rows, steps, warmup, budget_s=25.0):
+    """Times the reference's CPU kernels (oracle/_ref: its GEMV family, GEMM_CPU_FP32.cpp:14879-16838) on the
+    given dense weights; falls back to the C restatement when the compiled reference cannot run here.
+    Returns (seconds per product, description dict)."""
+    import oracle
+
+    K, N = weights[0].shape
+    M = x_rows.shape[0]
+    r = oracle.ref()
+    cores = os.cpu_count() or 1
+    if r is None:
+        # C restatement, single thread: dense walk of the ternary matrix (oracle.c, orc_dense_f64)
+        w = weights[0]
+        t0 = time.perf_counter()
+        oracle.dense_f64(x_rows.astype(np.float64), w, 1.0)
+        dt = time.perf_counter() - t0
+        return dt, {"kind": "port", "cores": 1, "kernel": "orc_dense_f64", "sample": f"1 product of {M}x{K}x{N}, 1 thread"}
+    r.ref_set_threads(cores)
+    x32 = np.ascontiguousarray(x_rows.astype(np.float32))
+    best = None
+    t_begin = time.perf_counter()
+    for G, name, simd in GEMV_CANDIDATES:
+        if N % G or time.perf_counter() - t_begin > budget_s:
+            continue
+        fmts = []
+        for w in weights:
+            meta, ri = oracle.ref_merged_group(w, G, "min", False, simd)
+            fmts.append((meta, np.concatenate([ri.astype(np.int32), np.zeros(64, np.int32)])))
+        y = np.zeros(N, np.float32)
+
+        def one_pass():
+            for meta, ri32 in fmts:
+                for m in range(M):          # the reference's decode path is one GEMV per row
+                    oracle.ref_call("F4", name, x32[m], meta, ri32, y, N, K)
+
+        try:
+            for _ in range(max(1, warmup)):
+                one_pass()
+        except KeyError:
+            continue
+        n = 0
+        t0 = time.perf_counter()
+        while n < steps and time.perf_counter() - t0 < budget_s / len(GEMV_CANDIDATES):
+            one_pass()
+            n += 1
+        dt = (time.perf_counter() - t0) / (n * len(fmts))
+        if best is None or dt < best[0]:
+            best = (dt, name, n)
+    dt, name, n = best
+    return dt, {"kind": "reference", "cores": cores, "kernel": name,
+                "sample": f"{n} passes over {len(weights)} distinct weights of {K}x{N}, {M} row(s), best of {len(GEMV_CANDIDATES)} reference GEMV kernels"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--sparsity", type=float, default=0.75)
+    ap.add_argument("--copies", type=int, default=0, help="distinct packed weights per step (0 = enough to exceed 3x L2)")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    M, K, N, S = a.rows, K_IN, N_OUT, a.sparsity
+    workload = f"decode ternary SpMV, Llama-7B up-projection shape: x[{M},{K}] fp16 N(0,1), W[{K},{N}] ternary {S:.0%} zeros, fp16 scale U(0.01,0.05)"
+
+    if a.impl == "reference":
+        if rank != 0:
+            return 0
+        weights = [make_weight(1000 + i, K, N, S) for i in range(4)]
+        nnz = int(np.mean([(w != 0).sum() for w in weights]))
+        rng = np.random.default_rng(12345)
+        x = rng.standard_normal((M, K)).astype(np.float16)
+        dt, desc = cpu_reference_run(weights, x, a.steps, a.warmup, budget_s=120.0)
+        balg = algorithmic_bytes(nnz, K, N, M, 2)
+        gbps = balg / dt / 1e9
+        line = {"impl": "reference", "metric": METRIC, "value": gbps, "unit": "GB/s", "n_gpus": a.gpus, "steps": a.steps,
+                "warmup": a.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic",
+                "config": {"workload": workload, "step": "one product on the host cores", "algorithmic_bytes_per_product": balg},
+                "cpu_baseline": {"value": gbps, "unit": "GB/s", **desc},
+                "e2e": {"value": gbps, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+        print(json.dumps(line))
+        return 0
+
+    import torch
+
+    from ternaryllm_b200 import PackedWeight, _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path in this library)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    peak, peak_kind = measured_peak()
+    R = a.copies or max(4, -(-3 * L2_BYTES // (2 * int(K * N * (1 - S)))) + 1)
+    rng = np.random.default_rng(12345)
+    scales = [float(np.float16(v)) for v in rng.uniform(0.01, 0.05, R)]
+    packed, nnzs, w0 = [], [], None
+    for i in range(R):
+        w = make_weight(1000 + 100 * rank + i, K, N, S)
+        nnzs.append(int((w != 0).sum()))
+        packed.append(PackedWeight.from_dense(w, scale=scales[i], device=device))
+        if i == 0:
+            w0 = w
+    nnz = int(np.mean(nnzs))
+    info = packed[0].info
+    balg = algorithmic_bytes(nnz, K, N, M, 2)
+    bphys = info["stream_bytes"] + info["meta_bytes"] + 2 * M * (K + N)
+
+    x_host = torch.tensor(rng.standard_normal((M, K)), dtype=torch.float16).pin_memory()
+    X = x_host.to(device)
+    Y = [torch.empty((M, N), dtype=torch.float16, device=device) for _ in range(R)]
+
+    def step():
+        for i in range(R):
+            packed[i].matmul(X, out=Y[i])
+
+    # correctness guard inside the benchmark: compare one product with a dense fp64 product on the device
+    step()
+    torch.cuda.synchronize()
+    ref = (X.double() @ torch.tensor(w0, device=device).double()) * scales[0]
+    err = float((Y[0].double() - ref).abs().max() / ref.abs().max())
+    if not err <= 1e-3 + 2.0 ** -11:
+        raise SystemExit(f"benchmark output differs from the dense product (rel err {err})")
+
+    graph = None
+    if not a.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+        except Exception as e:      # keep measuring with plain launches
+            sys.stderr.write(f"[bench] CUDA graph capture failed ({e}); timing plain launches\n")
+            graph = None
+            torch.cuda.synchronize()
+    run = graph.replay if graph is not None else step
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(a.warmup):
+        run()
+    barrier()
+    launches0 = _lib.lib().tllm_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clk:
+        e0.record()
+        for _ in range(a.steps):
+            run()
+        e1.record()
+        barrier()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / a.steps
+    us_launch = ms_step * 1e3 / R
+    gpu_launches = a.steps * R            # R kernel launches per step (replayed from a graph when one was captured)
+    value = world * R * balg / (ms_step * 1e-3) / 1e9
+    achieved = balg / (us_launch * 1e-6) / 1e9
+    for p in packed:
+        p.check()
+
+    # ---- end to end through the host-buffer entry point ----
+    y_host = [np.empty((M, N), np.float16) for _ in range(R)]
+    y_pin = [torch.from_numpy(y).pin_memory() for y in y_host]
+    e2e_steps = max(3, min(a.steps, 100))
+
+    def e2e_step():
+        for i in range(R):
+            _lib.check(_lib.lib().tllm_spmm_host(packed[i]._h, x_host.data_ptr(), _lib.F16, _lib.ROW_MAJOR, M, y_pin[i].data_ptr(),
+                                                 _lib.F16, _lib.ROW_MAJOR))
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    dt_e2e = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([dt_e2e], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt_e2e = float(t.item())
+    e2e_val = world * R * balg / dt_e2e / 1e9
+    err2 = float((y_pin[0].to(device).double() - ref).abs().max() / ref.abs().max())
+    if not err2 <= 1e-3 + 2.0 ** -11:
+        raise SystemExit(f"host-buffer path differs from the dense product (rel err {err2})")
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": workload, "step": f"one decode token through {R} distinct packed weights ({R} launches)",
+                   "l2": f"inputs larger than L2: {R} weights x {bphys / 1e6:.1f} MB rotate through a {L2_BYTES >> 20} MiB L2",
+                   "algorithmic_bytes_per_launch": balg, "physical_bytes_per_launch": bphys, "nnz": nnz,
+                   "us_per_launch": us_launch, "cuda_graph": graph is not None, "pdl": os.environ.get("TLLM_PDL", "1") != "0",
+                   "accumulate": "fp32", "check_rel_err": err,
+                   "pack": {k: info[k] for k in ("tile_rows", "tiles", "col_blocks", "k_splits", "num_ctas", "lanes_per_list")}},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "frac_physical": (bphys / (us_launch * 1e-6) / 1e9) / peak, "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
+                     "traffic": NCU_TRAFFIC_BYTES},
+        "clocks": clk.summary(),
+        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": R * 2 * M * K, "d2h_bytes_per_step": R * 2 * M * N,
+                "us_per_call": dt_e2e * 1e6 / R, "steps": e2e_steps},
+        "gpu_launches": gpu_launches,
+    }
+    if world == 1 and not a.no_cpu_baseline:
+        try:
+            cw = [w0] + [make_weight(1000 + i, K, N, S) for i in range(1, 4)]
+            dt, desc = cpu_reference_run(cw, x_host.numpy(), 10, 3, budget_s=20.0)
+            line["cpu_baseline"] = {"value": balg / dt / 1e9, "unit": "GB/s", "us_per_product": dt * 1e6, **desc}
+        except Exception as e:
+            line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,186 @@
+/*
+ * tllm.h -- C ABI of the B200-native ternary sparse product  Y = X . W . s,  W in {-1,0,+1}.
+ *
+ * Plain C, plain pointers and sizes; no torch or C++ types cross this boundary.  Every entry point
+ * below replaces one interface of fpgasystems/ternaryLLM; the citation (path within that repository,
+ * file:line) says which.  All functions return 0 on success and a negative code on failure;
+ * tllm_last_error() then holds a message for the calling thread.  Nothing here falls back to a CPU
+ * implementation: a missing or unusable CUDA device is an error.
+ */
+#ifndef TLLM_H_
+#define TLLM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TLLM_OK 0
+#define TLLM_ERR_ARG (-1)      /* bad argument / unsupported shape */
+#define TLLM_ERR_CUDA (-2)     /* a CUDA runtime call failed */
+#define TLLM_ERR_KERNEL (-3)   /* a kernel reported a bounded wait that ran out (see tllm_last_error) */
+#define TLLM_ERR_NOMEM (-4)
+
+/* element types of activations / results */
+#define TLLM_F32 0
+#define TLLM_F16 1
+#define TLLM_BF16 2
+#define TLLM_I8 3              /* int8 activations, exact int32 accumulation */
+#define TLLM_I32 4             /* result type for TLLM_I8 activations */
+
+/* activation layouts */
+#define TLLM_ROW_MAJOR 0       /* X is [M][K], K contiguous (what the reference's Python modules hold) */
+#define TLLM_COL_MAJOR 1       /* X is [K][M], M contiguous (what ter_tiled_mcsc_spmm indexes,
+                                  ternaryLLM_GPU/csrc/ter_spmm_kernel.cuh:173, and what the col-major CPU
+                                  kernels take, ternaryLLM_CPU/src/GEMM_CPU_FP32.cpp:509-538) */
+
+const char* tllm_last_error(void);
+int tllm_version(void);
+/* number of kernels this library has launched in the calling process (for benchmarks' bookkeeping) */
+int64_t tllm_launch_count(void);
+
+/* --------------------------------------------------------------------------------------------------
+ * Host-side packers: the four callables of the reference's `ter_spmm` extension module
+ * (ternaryLLM_GPU/csrc/ter_spmm_wrapper.cu:350-355).  w is int32 [inners][columns] row-major on the
+ * host with entries in {-1,0,1}; outputs are caller-allocated.
+ * -------------------------------------------------------------------------------------------------- */
+
+/* counts of +1 / -1 entries (TernaryLinear.py:104-105) */
+int tllm_count_nnz(const int32_t* w, int columns, int inners, int64_t* cnt_pos, int64_t* cnt_neg);
+
+/* convert_to_ter_csc (ter_spmm_wrapper.cu:39-78): neg_idx[cnt_neg], neg_off[columns+1],
+ * pos_idx[cnt_pos], pos_off[columns+1] -- the reference returns them in this order. */
+int tllm_convert_to_ter_csc(const int32_t* w, int columns, int inners, int32_t* neg_idx, int32_t* neg_off,
+                            int32_t* pos_idx, int32_t* pos_off);
+
+/* convert_to_ter_tiled_csc (ter_spmm_wrapper.cu:92-152): tile-local ids and [start,end) per
+ * (column, tile): neg_off / pos_off hold columns*ceil(inners/tile_k)*2 entries.  Rows past `inners`
+ * in the last tile count as zero (the reference reads out of bounds there). */
+int tllm_convert_to_ter_tiled_csc(const int32_t* w, int columns, int inners, int tile_k, int32_t* neg_idx,
+                                  int32_t* neg_off, int32_t* pos_idx, int32_t* pos_off);
+
+/* convert_to_ter_tiled_mcsc (ter_spmm_wrapper.cu:156-315): merged tiled CSC.
+ *   mode 0: lossless (the behaviour of the reference's Python twin, TernaryCSC.py:97-156); `padding`
+ *           pads the pair region of every list with neutral (p,p) pairs to a multiple of padding_size
+ *           and never drops an entry.
+ *   mode 1: bit-compatible with the reference's C++ packer, including its truncation of list lengths
+ *           to multiples of four (:277-291).  For drop-in comparisons only: it does not encode W.
+ * tllm_ter_tiled_mcsc_len gives the number of row-index entries to allocate.  off has
+ * columns*tiles*4 entries {pair_start, pair_end, rem_end, sign}; tile_idx (columns*tiles, may be NULL)
+ * receives the per-column tile order by list length (inter_tile_swizzle, :9-27). */
+int64_t tllm_ter_tiled_mcsc_len(const int32_t* w, int columns, int inners, int tile_k, int padding,
+                                int padding_size, int mode);
+int tllm_convert_to_ter_tiled_mcsc(const int32_t* w, int columns, int inners, int tile_k, int padding,
+                                   int padding_size, int mode, int32_t* row_idx, int64_t row_idx_cap,
+                                   int32_t* off, int32_t* tile_idx);
+
+/* --------------------------------------------------------------------------------------------------
+ * ter_spmm on the reference's own arrays (ter_spmm_wrapper.cu:318-348 -> ter_spmm_kernel.cuh:510-531).
+ * All pointers are DEVICE pointers.  X holds `batch` matrices of rows x inners (layout as given);
+ * Y receives batch x rows x columns, row-major, in y_dtype.  row_idx are int16 tile-local ids, col_off
+ * the four int32 per (column, tile); col_tile_idx is accepted and unused, like in the reference
+ * (ter_spmm_kernel.cuh:159-160).  Every list entry is honoured (pairs, then sign * remainder, with the
+ * tile base applied to both), whatever `uniformed` / `padded` say.  Launches on `stream`
+ * (a cudaStream_t; NULL = legacy default stream); no allocation, no synchronisation.
+ * -------------------------------------------------------------------------------------------------- */
+int tllm_ter_spmm(const void* X, int x_dtype, int x_layout, const int16_t* row_idx, const int32_t* col_off,
+                  const int16_t* col_tile_idx, void* Y, int y_dtype, int batch, int rows, int columns,
+                  int inners, int tile_k, float scale, int uniformed, int padded, void* stream);
+
+/* --------------------------------------------------------------------------------------------------
+ * Packed weights in the library's own B200 stream format (the replacement for
+ * convert_ternary_weights + the three TernaryLinear buffers, TernaryLinear.py:87-113,144-146), and the
+ * product on them (the replacement for TernaryLinear.forward, :152-182).
+ * -------------------------------------------------------------------------------------------------- */
+typedef struct tllm_weight tllm_weight;
+
+typedef struct tllm_pack_opts {
+    int tile_rows;        /* rows of W covered by one shared-memory activation table; 0 = default (1024) */
+    int num_ctas;         /* thread blocks to schedule for; 0 = number of SMs of the current device */
+    int lanes_per_list;   /* lanes that share one index list (power of two, 1..16); 0 = choose from density */
+    int max_rows;         /* largest M a single call may pass (scratch is sized for it); 0 = 16 */
+    int reserved[4];
+} tllm_pack_opts;
+
+typedef struct tllm_weight_info {
+    int inners, columns, tile_rows, tiles, col_blocks, k_splits, tiles_per_cta, num_ctas, lanes_per_list;
+    int max_rows;
+    int64_t nnz;               /* true non-zeros of W */
+    int64_t stream_bytes;      /* index stream as stored (with padding) */
+    int64_t meta_bytes;        /* list-offset metadata as stored */
+    int64_t scratch_bytes;     /* split-K partial sums + counters owned by the handle */
+    int64_t algorithmic_bytes; /* 2*nnz + 16*columns*ceil(inners/512): the reference layout's weight bytes */
+    float scale;
+} tllm_weight_info;
+
+/* from a dense ternary matrix, int8 [inners][columns] row-major, host memory */
+int tllm_weight_create_dense(const int8_t* w, int inners, int columns, float scale,
+                             const tllm_pack_opts* opts, tllm_weight** out);
+/* from the reference's merged tiled CSC arrays on the host (row ids as int32, as the packers return them) */
+int tllm_weight_create_mcsc(const int32_t* row_idx, const int32_t* col_off, int columns, int inners,
+                            int tile_k, float scale, const tllm_pack_opts* opts, tllm_weight** out);
+/* from the reference's CPU formats (ternaryLLM_CPU/src/TCSC.hpp), host memory:
+ *   kind 0 SparseFormat (:6-34): meta = col_start_neg[N+1] ++ col_start_pos[N+1], ri = neg ids ++ pos ids,
+ *          aux = number of neg ids
+ *   kind 1 MergedTCSC (:36-90); kind 2/3/4 MergedTCSC_Group "min"/"mid"/"max" (:92-409);
+ *   kind 5 uniform (meta[0] = non-zeros per column).
+ * group = columns per group; chunk = 0 for the column-interleaved prefix, otherwise the number of
+ * consecutive positives (then negatives) per block (group size for interleaved=false, 8 / 16 for the
+ * _CS8 / _CS16 layouts); ri32 selects int32 row ids. */
+int tllm_weight_create_cpu_format(int kind, int group, int chunk, const int32_t* meta, const void* ri,
+                                  int ri32, int64_t aux, int columns, int inners, float scale,
+                                  const tllm_pack_opts* opts, tllm_weight** out);
+/* Diagnostic that needs no GPU: packs w for `num_sms` thread blocks on the host, checks the invariants the
+ * kernel relies on (lists tile every block's range exactly, every work unit fits the ring, every ring stage
+ * is handed back exactly once), unpacks into w_out (inners*columns int8) and fills info. */
+int tllm_pack_roundtrip(const int8_t* w, int inners, int columns, const tllm_pack_opts* opts, int num_sms,
+                        int8_t* w_out, tllm_weight_info* info);
+int tllm_weight_destroy(tllm_weight* w);
+int tllm_weight_get_info(const tllm_weight* w, tllm_weight_info* info);
+/* change the per-tensor scale s (host value; takes effect for later calls) */
+int tllm_weight_set_scale(tllm_weight* w, float scale);
+
+/* Reads the handle's device status word (this synchronises with the device).  Returns TLLM_ERR_KERNEL if
+ * a kernel gave up on one of its bounded waits since the last check -- its output is then undefined --
+ * and clears the condition. */
+int tllm_weight_check(tllm_weight* w);
+
+/* Y[rows][columns] = X . W . s   on device pointers, launched on `stream`.  rows <= max_rows of the
+ * handle per launch; larger row counts are processed in chunks.  Calls on one handle must not overlap
+ * on the GPU (they share the handle's scratch); calls on different handles may. */
+int tllm_spmm(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y, int y_dtype,
+              void* stream);
+
+/* Same with HOST buffers: copies X to the device, runs, copies Y back and synchronises.  This is the
+ * form behind the CPU entry points (GEMM_CPU_FP32.hpp:40-185, GEMM_CPU_INT8.hpp:11-29): caller-owned host
+ * arrays in, host arrays out.  y_layout TLLM_COL_MAJOR writes Y as [columns][rows], the col-major
+ * kernels' result layout (GEMM_CPU_FP32.cpp:534). */
+int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y, int y_dtype,
+                   int y_layout);
+
+/* --------------------------------------------------------------------------------------------------
+ * Fused ternary MLP block  y = down( silu(gate(x)) * up(x) )  (TernaryMLP.py:33-35;
+ * TernaryMLP<T>::forward, ternaryLLM_CPU/src/LlamaModel.hpp:343-452): gate and up share one activation
+ * table and one launch whose epilogue applies SiLU and the product; down follows as a dependent launch
+ * whose weight stream is prefetched while the first kernel drains.
+ * -------------------------------------------------------------------------------------------------- */
+typedef struct tllm_mlp tllm_mlp;
+int tllm_mlp_create(const int8_t* w_gate, const int8_t* w_up, const int8_t* w_down, int hidden,
+                    int intermediate, float s_gate, float s_up, float s_down, const tllm_pack_opts* opts,
+                    tllm_mlp** out);
+int tllm_mlp_destroy(tllm_mlp* m);
+/* X [rows][hidden] -> Y [rows][hidden]; H (device, rows*intermediate elements of x_dtype) receives the
+ * intermediate activations and may be NULL to use the handle's own buffer. */
+int tllm_mlp_forward(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y, void* H, void* stream);
+int tllm_mlp_get_info(const tllm_mlp* m, tllm_weight_info* gate_up, tllm_weight_info* down);
+
+/* Exact SiLU(x)*y epilogue on its own (Naive_SiLU_Dot, ternaryLLM_CPU/src/initData.hpp:204-210):
+ * g[i] = g[i]*u[i]/(1+exp(-g[i])) in fp32, device pointers. */
+int tllm_silu_mul(void* g, const void* u, int dtype, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TLLM_H_ */

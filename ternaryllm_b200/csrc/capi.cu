@@ -1,0 +1,489 @@
+// capi.cu -- the C ABI of libtllm (declared in include/tllm.h): handles, launches, host staging.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "kernels.cuh"
+#include "util.h"
+
+namespace tllm {
+
+static thread_local std::string g_err;
+static std::atomic<int64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+
+#define CU_TRY(expr)                                                                                       \
+    do {                                                                                                   \
+        cudaError_t e_ = (expr);                                                                           \
+        if (e_ != cudaSuccess) return fail(TLLM_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
+    } while (0)
+
+static size_t dtype_size(int dt) {
+    switch (dt) {
+        case TLLM_F32: case TLLM_I32: return 4;
+        case TLLM_F16: case TLLM_BF16: return 2;
+        case TLLM_I8: return 1;
+    }
+    return 0;
+}
+
+static bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("TLLM_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+}  // namespace tllm
+
+using namespace tllm;
+
+struct tllm_weight {
+    TsLayout lay;
+    float scale = 1.f;
+    int device = 0;
+    int max_rows = 16;
+    uint4* d_stream = nullptr;
+    uint32_t* d_vstart = nullptr;
+    void* d_partial = nullptr;
+    unsigned int* d_counters = nullptr;
+    int* d_status = nullptr;
+    size_t stream_bytes = 0, meta_bytes = 0, scratch_bytes = 0;
+    // staging for the host-buffer entry point
+    void* d_x = nullptr;
+    void* d_y = nullptr;
+    void* h_pin = nullptr;
+    size_t x_cap = 0, y_cap = 0, pin_cap = 0;
+    cudaStream_t own_stream = nullptr;
+};
+
+struct tllm_mlp {
+    tllm_weight* gate_up = nullptr;   // columns interleaved: 2c = gate column c, 2c+1 = up column c
+    tllm_weight* down = nullptr;
+    int hidden = 0, inter = 0;
+    float s_gate = 1.f, s_up = 1.f;
+    void* d_h = nullptr;
+    size_t h_cap = 0;
+};
+
+namespace {
+
+template <typename ACC, int MP, int NW>
+int launch_ts(const TsParams& p, int grid, size_t smem, cudaStream_t st) {
+    auto kern = tstream_spmm_kernel<ACC, MP, NW>;
+    static std::mutex mu;
+    static bool configured[64] = {};
+    int dev = 0;
+    CU_TRY(cudaGetDevice(&dev));
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (dev < 64 && !configured[dev]) {
+            CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            configured[dev] = true;
+        }
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3((NW + 1) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    CU_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return TLLM_OK;
+}
+
+template <typename ACC>
+int dispatch_ts(const TsParams& p, int grid, size_t smem, cudaStream_t st) {
+    if (p.M <= 1) return launch_ts<ACC, 1, 31>(p, grid, smem, st);
+    if (p.M <= 2) return launch_ts<ACC, 2, 31>(p, grid, smem, st);
+    if (p.M <= 4) return launch_ts<ACC, 4, 31>(p, grid, smem, st);
+    if (p.M <= 8) return launch_ts<ACC, 8, 15>(p, grid, smem, st);
+    return launch_ts<ACC, 16, 15>(p, grid, smem, st);
+}
+
+int check_types(int x_dtype, int y_dtype, const char* who) {
+    if (x_dtype == TLLM_I8) {
+        if (y_dtype != TLLM_I32) return fail(TLLM_ERR_ARG, "%s: int8 activations produce int32 results (y_dtype must be TLLM_I32)", who);
+        return TLLM_OK;
+    }
+    if (x_dtype != TLLM_F32 && x_dtype != TLLM_F16 && x_dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "%s: unsupported x_dtype %d", who, x_dtype);
+    if (y_dtype != TLLM_F32 && y_dtype != TLLM_F16 && y_dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "%s: unsupported y_dtype %d", who, y_dtype);
+    return TLLM_OK;
+}
+
+// one launch of at most max_rows rows
+int run_ts(tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, int rows, void* Y, int y_dtype, int y_ld,
+           int epilogue, float scale, float scale2, cudaStream_t st) {
+    const TsLayout& L = w->lay;
+    TsParams p{};
+    p.stream = w->d_stream;
+    p.vstart = w->d_vstart;
+    p.X = X;
+    p.Y = Y;
+    p.partial = w->d_partial;
+    p.counters = w->d_counters;
+    p.status = w->d_status;
+    p.x_dtype = x_dtype;
+    p.x_layout = x_layout;
+    p.y_dtype = y_dtype;
+    p.M = rows;
+    p.K = L.inners;
+    p.N = L.columns;
+    p.T = L.tile_rows;
+    p.tiles = L.tiles;
+    p.col_blocks = L.col_blocks;
+    p.cols_per_block = L.cols_per_block;
+    p.k_splits = L.k_splits;
+    p.tiles_per_cta = L.tiles_per_cta;
+    int lg = 0;
+    while ((1 << lg) < L.lanes_per_list) ++lg;
+    p.lpl_log2 = lg;
+    p.nstages = TS_MAX_STAGES;
+    p.epilogue = epilogue;
+    p.y_ld = y_ld;
+    p.x_ld = x_ld;
+    p.scale = scale;
+    p.scale2 = scale2;
+    std::memcpy(p.cta, L.cta, sizeof(TsCtaDesc) * (size_t)L.num_ctas);
+    const TsSmem sm = ts_smem_layout(TS_MAX_TILE_ROWS, TS_MAX_STAGES, TS_MAX_META_BYTES);
+    if (x_dtype == TLLM_I8) return dispatch_ts<int>(p, L.num_ctas, sm.total, st);
+    return dispatch_ts<float>(p, L.num_ctas, sm.total, st);
+}
+
+int upload(tllm_weight* w, const TsHostImage& img, float scale, int max_rows) {
+    w->lay = img.lay;
+    w->scale = scale;
+    w->max_rows = max_rows;
+    CU_TRY(cudaGetDevice(&w->device));
+    // one stage of slack behind the stream: the last bulk copy of a block never reads past its own range,
+    // but keeping the allocation a multiple of a stage makes that independent of packer details
+    w->stream_bytes = img.stream.size() * sizeof(uint16_t);
+    w->meta_bytes = img.vstart.size() * sizeof(uint32_t);
+    CU_TRY(cudaMalloc(&w->d_stream, w->stream_bytes + TS_STAGE_VECS * 16));
+    CU_TRY(cudaMalloc(&w->d_vstart, w->meta_bytes + 16));
+    CU_TRY(cudaMemcpy(w->d_stream, img.stream.data(), w->stream_bytes, cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemcpy(w->d_vstart, img.vstart.data(), w->meta_bytes, cudaMemcpyHostToDevice));
+    const size_t partial_bytes = (size_t)img.lay.k_splits * max_rows * img.lay.columns * 4;
+    const size_t counter_bytes = (size_t)img.lay.col_blocks * sizeof(unsigned int);
+    w->scratch_bytes = partial_bytes + counter_bytes + sizeof(int);
+    CU_TRY(cudaMalloc(&w->d_partial, partial_bytes));
+    CU_TRY(cudaMalloc(&w->d_counters, counter_bytes));
+    CU_TRY(cudaMalloc(&w->d_status, sizeof(int)));
+    CU_TRY(cudaMemset(w->d_counters, 0, counter_bytes));
+    CU_TRY(cudaMemset(w->d_status, 0, sizeof(int)));
+    CU_TRY(cudaDeviceSynchronize());
+    return TLLM_OK;
+}
+
+int create_from_dense(const int8_t* dense, int inners, int columns, float scale, const tllm_pack_opts* opts, tllm_weight** out) {
+    if (!out) return fail(TLLM_ERR_ARG, "weight create: out is NULL");
+    *out = nullptr;
+    int dev = 0, sms = 0;
+    CU_TRY(cudaGetDevice(&dev));
+    CU_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int max_smem = 0;
+    CU_TRY(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    const TsSmem sm = ts_smem_layout(TS_MAX_TILE_ROWS, TS_MAX_STAGES, TS_MAX_META_BYTES);
+    if ((int)sm.total > max_smem)
+        return fail(TLLM_ERR_ARG, "this device offers %d bytes of shared memory per block; the kernel needs %u (built for sm_100a)", max_smem, sm.total);
+    TsHostImage img;
+    if (sms > TS_MAX_CTAS) sms = TS_MAX_CTAS;
+    const char* msg = ts_pack_dense(dense, inners, columns, opts, sms, &img);
+    if (msg) return fail(TLLM_ERR_ARG, "%s", msg);
+    int max_rows = (opts && opts->max_rows > 0) ? opts->max_rows : 16;
+    if (max_rows > 16) max_rows = 16;
+    tllm_weight* w = new tllm_weight();
+    const int rc = upload(w, img, scale, max_rows);
+    if (rc != TLLM_OK) {
+        tllm_weight_destroy(w);
+        return rc;
+    }
+    *out = w;
+    return TLLM_OK;
+}
+
+int ensure(void** p, size_t* cap, size_t need, bool pinned) {
+    if (*cap >= need) return TLLM_OK;
+    if (*p) {
+        if (pinned) CU_TRY(cudaFreeHost(*p));
+        else CU_TRY(cudaFree(*p));
+        *p = nullptr;
+        *cap = 0;
+    }
+    size_t n = need < 4096 ? 4096 : need;
+    if (pinned) CU_TRY(cudaMallocHost(p, n));
+    else CU_TRY(cudaMalloc(p, n));
+    *cap = n;
+    return TLLM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* tllm_last_error(void) { return g_err.c_str(); }
+int tllm_version(void) { return 100; }
+int64_t tllm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int tllm_ter_spmm(const void* X, int x_dtype, int x_layout, const int16_t* row_idx, const int32_t* col_off,
+                  const int16_t* col_tile_idx, void* Y, int y_dtype, int batch, int rows, int columns,
+                  int inners, int tile_k, float scale, int uniformed, int padded, void* stream) {
+    (void)col_tile_idx;
+    (void)uniformed;
+    (void)padded;
+    if (!X || !row_idx || !col_off || !Y) return fail(TLLM_ERR_ARG, "tllm_ter_spmm: NULL pointer");
+    if (batch < 0 || rows <= 0 || columns <= 0 || inners <= 0 || tile_k <= 0) return fail(TLLM_ERR_ARG, "tllm_ter_spmm: bad shape");
+    const int rc = check_types(x_dtype, y_dtype, "tllm_ter_spmm");
+    if (rc) return rc;
+    if (batch == 0) return TLLM_OK;   // the reference launches nothing for a 2-D input (TernaryLinear.py:168)
+    if (batch > 65535) return fail(TLLM_ERR_ARG, "tllm_ter_spmm: batch too large");
+    constexpr int MC = 4;
+    dim3 grid((columns + 7) / 8, (rows + MC - 1) / MC, batch), block(256);
+    if (grid.y > 65535) return fail(TLLM_ERR_ARG, "tllm_ter_spmm: too many rows for one call");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_dtype == TLLM_I8)
+        mcsc_spmm_kernel<int, MC><<<grid, block, 0, st>>>(X, x_dtype, x_layout, row_idx, col_off, Y, y_dtype, rows, columns, inners, tile_k, scale);
+    else
+        mcsc_spmm_kernel<float, MC><<<grid, block, 0, st>>>(X, x_dtype, x_layout, row_idx, col_off, Y, y_dtype, rows, columns, inners, tile_k, scale);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return TLLM_OK;
+}
+
+int tllm_weight_create_dense(const int8_t* w, int inners, int columns, float scale, const tllm_pack_opts* opts, tllm_weight** out) {
+    if (!w || inners <= 0 || columns <= 0) return fail(TLLM_ERR_ARG, "tllm_weight_create_dense: bad argument");
+    const size_t n = (size_t)inners * columns;
+    for (size_t i = 0; i < n; ++i)
+        if (w[i] < -1 || w[i] > 1) return fail(TLLM_ERR_ARG, "tllm_weight_create_dense: entry %zu is %d, not ternary", i, (int)w[i]);
+    return create_from_dense(w, inners, columns, scale, opts, out);
+}
+
+int tllm_weight_create_mcsc(const int32_t* row_idx, const int32_t* col_off, int columns, int inners, int tile_k, float scale,
+                            const tllm_pack_opts* opts, tllm_weight** out) {
+    if (!row_idx || !col_off || columns <= 0 || inners <= 0 || tile_k <= 0) return fail(TLLM_ERR_ARG, "tllm_weight_create_mcsc: bad argument");
+    std::vector<int8_t> dense;
+    const char* msg = decode_mcsc(row_idx, col_off, columns, inners, tile_k, &dense);
+    if (msg) return fail(TLLM_ERR_ARG, "%s", msg);
+    return create_from_dense(dense.data(), inners, columns, scale, opts, out);
+}
+
+int tllm_weight_create_cpu_format(int kind, int group, int chunk, const int32_t* meta, const void* ri, int ri32, int64_t aux,
+                                  int columns, int inners, float scale, const tllm_pack_opts* opts, tllm_weight** out) {
+    if (!meta || !ri || columns <= 0 || inners <= 0) return fail(TLLM_ERR_ARG, "tllm_weight_create_cpu_format: bad argument");
+    std::vector<int8_t> dense;
+    const char* msg = decode_cpu_format(kind, group, chunk, meta, ri, ri32, aux, columns, inners, &dense);
+    if (msg) return fail(TLLM_ERR_ARG, "%s", msg);
+    return create_from_dense(dense.data(), inners, columns, scale, opts, out);
+}
+
+int tllm_weight_destroy(tllm_weight* w) {
+    if (!w) return TLLM_OK;
+    cudaFree(w->d_stream);
+    cudaFree(w->d_vstart);
+    cudaFree(w->d_partial);
+    cudaFree(w->d_counters);
+    cudaFree(w->d_status);
+    cudaFree(w->d_x);
+    cudaFree(w->d_y);
+    if (w->h_pin) cudaFreeHost(w->h_pin);
+    if (w->own_stream) cudaStreamDestroy(w->own_stream);
+    delete w;
+    return TLLM_OK;
+}
+
+int tllm_weight_get_info(const tllm_weight* w, tllm_weight_info* info) {
+    if (!w || !info) return fail(TLLM_ERR_ARG, "tllm_weight_get_info: NULL");
+    const TsLayout& L = w->lay;
+    info->inners = L.inners;
+    info->columns = L.columns;
+    info->tile_rows = L.tile_rows;
+    info->tiles = L.tiles;
+    info->col_blocks = L.col_blocks;
+    info->k_splits = L.k_splits;
+    info->tiles_per_cta = L.tiles_per_cta;
+    info->num_ctas = L.num_ctas;
+    info->lanes_per_list = L.lanes_per_list;
+    info->max_rows = w->max_rows;
+    info->nnz = L.nnz;
+    info->stream_bytes = (int64_t)w->stream_bytes;
+    info->meta_bytes = (int64_t)w->meta_bytes;
+    info->scratch_bytes = (int64_t)w->scratch_bytes;
+    info->algorithmic_bytes = 2 * L.nnz + 16 * (int64_t)L.columns * ((L.inners + 511) / 512);
+    info->scale = w->scale;
+    return TLLM_OK;
+}
+
+int tllm_weight_set_scale(tllm_weight* w, float scale) {
+    if (!w) return fail(TLLM_ERR_ARG, "tllm_weight_set_scale: NULL");
+    w->scale = scale;
+    return TLLM_OK;
+}
+
+int tllm_weight_check(tllm_weight* w) {
+    if (!w) return fail(TLLM_ERR_ARG, "tllm_weight_check: NULL");
+    int st = 0;
+    CU_TRY(cudaMemcpy(&st, w->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (st != 0) {
+        cudaMemset(w->d_status, 0, sizeof(int));
+        cudaMemset(w->d_counters, 0, (size_t)w->lay.col_blocks * sizeof(unsigned int));
+        return fail(TLLM_ERR_KERNEL, "a bounded wait ran out inside the kernel (code %d: %s)", st,
+                    st == TS_ERR_FULL_WAIT ? "index stream stage never arrived" : st == TS_ERR_EMPTY_WAIT ? "ring stage never released" : "list table never arrived");
+    }
+    return TLLM_OK;
+}
+
+int tllm_spmm(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y, int y_dtype, void* stream) {
+    if (!w || !X || !Y) return fail(TLLM_ERR_ARG, "tllm_spmm: NULL pointer");
+    if (rows <= 0) return fail(TLLM_ERR_ARG, "tllm_spmm: rows must be positive");
+    if (x_layout != TLLM_ROW_MAJOR && x_layout != TLLM_COL_MAJOR) return fail(TLLM_ERR_ARG, "tllm_spmm: bad x_layout");
+    const int rc = check_types(x_dtype, y_dtype, "tllm_spmm");
+    if (rc) return rc;
+    const TsLayout& L = w->lay;
+    const size_t xe = dtype_size(x_dtype), ye = dtype_size(y_dtype);
+    const int x_ld = x_layout == TLLM_ROW_MAJOR ? L.inners : rows;
+    for (int r0 = 0; r0 < rows; r0 += w->max_rows) {
+        const int m = rows - r0 < w->max_rows ? rows - r0 : w->max_rows;
+        const char* xp = (const char*)X + (x_layout == TLLM_ROW_MAJOR ? (size_t)r0 * L.inners : (size_t)r0) * xe;
+        char* yp = (char*)Y + (size_t)r0 * L.columns * ye;
+        const int r = run_ts(w, xp, x_dtype, x_layout, x_ld, m, yp, y_dtype, L.columns, 0, w->scale, 0.f, (cudaStream_t)stream);
+        if (r) return r;
+    }
+    return TLLM_OK;
+}
+
+int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y, int y_dtype, int y_layout) {
+    if (!w || !X || !Y) return fail(TLLM_ERR_ARG, "tllm_spmm_host: NULL pointer");
+    if (rows <= 0) return fail(TLLM_ERR_ARG, "tllm_spmm_host: rows must be positive");
+    const int rc = check_types(x_dtype, y_dtype, "tllm_spmm_host");
+    if (rc) return rc;
+    const TsLayout& L = w->lay;
+    const size_t xb = (size_t)rows * L.inners * dtype_size(x_dtype), yb = (size_t)rows * L.columns * dtype_size(y_dtype);
+    if (!w->own_stream) CU_TRY(cudaStreamCreateWithFlags(&w->own_stream, cudaStreamNonBlocking));
+    int r = ensure(&w->d_x, &w->x_cap, xb, false);
+    if (r) return r;
+    r = ensure(&w->d_y, &w->y_cap, yb, false);
+    if (r) return r;
+    CU_TRY(cudaMemcpyAsync(w->d_x, X, xb, cudaMemcpyHostToDevice, w->own_stream));
+    r = tllm_spmm(w, w->d_x, x_dtype, x_layout, rows, w->d_y, y_dtype, w->own_stream);
+    if (r) return r;
+    if (y_layout == TLLM_ROW_MAJOR) {
+        CU_TRY(cudaMemcpyAsync(Y, w->d_y, yb, cudaMemcpyDeviceToHost, w->own_stream));
+        CU_TRY(cudaStreamSynchronize(w->own_stream));
+    } else {
+        r = ensure(&w->h_pin, &w->pin_cap, yb, true);
+        if (r) return r;
+        CU_TRY(cudaMemcpyAsync(w->h_pin, w->d_y, yb, cudaMemcpyDeviceToHost, w->own_stream));
+        CU_TRY(cudaStreamSynchronize(w->own_stream));
+        const size_t e = dtype_size(y_dtype);
+        const char* src = (const char*)w->h_pin;
+        char* dst = (char*)Y;
+        for (int m = 0; m < rows; ++m)
+            for (int n = 0; n < L.columns; ++n) std::memcpy(dst + ((size_t)n * rows + m) * e, src + ((size_t)m * L.columns + n) * e, e);
+    }
+    return tllm_weight_check(w);
+}
+
+int tllm_mlp_create(const int8_t* w_gate, const int8_t* w_up, const int8_t* w_down, int hidden, int intermediate, float s_gate,
+                    float s_up, float s_down, const tllm_pack_opts* opts, tllm_mlp** out) {
+    if (!w_gate || !w_up || !w_down || hidden <= 0 || intermediate <= 0 || !out) return fail(TLLM_ERR_ARG, "tllm_mlp_create: bad argument");
+    *out = nullptr;
+    std::vector<int8_t> gu((size_t)hidden * 2 * intermediate);
+    for (int k = 0; k < hidden; ++k) {
+        const int8_t* g = w_gate + (size_t)k * intermediate;
+        const int8_t* u = w_up + (size_t)k * intermediate;
+        int8_t* d = gu.data() + (size_t)k * 2 * intermediate;
+        for (int c = 0; c < intermediate; ++c) {
+            d[2 * c] = g[c];
+            d[2 * c + 1] = u[c];
+        }
+    }
+    tllm_mlp* m = new tllm_mlp();
+    m->hidden = hidden;
+    m->inter = intermediate;
+    m->s_gate = s_gate;
+    m->s_up = s_up;
+    int rc = tllm_weight_create_dense(gu.data(), hidden, 2 * intermediate, 1.f, opts, &m->gate_up);
+    if (rc == TLLM_OK) rc = tllm_weight_create_dense(w_down, intermediate, hidden, s_down, opts, &m->down);
+    if (rc == TLLM_OK && (m->gate_up->lay.cols_per_block & 1)) rc = fail(TLLM_ERR_ARG, "tllm_mlp_create: internal: odd column block");
+    if (rc == TLLM_OK) {
+        m->h_cap = (size_t)16 * intermediate * 4;
+        cudaError_t e = cudaMalloc(&m->d_h, m->h_cap);
+        if (e != cudaSuccess) rc = fail(TLLM_ERR_CUDA, "cudaMalloc failed: %s", cudaGetErrorString(e));
+    }
+    if (rc != TLLM_OK) {
+        tllm_mlp_destroy(m);
+        return rc;
+    }
+    *out = m;
+    return TLLM_OK;
+}
+
+int tllm_mlp_destroy(tllm_mlp* m) {
+    if (!m) return TLLM_OK;
+    tllm_weight_destroy(m->gate_up);
+    tllm_weight_destroy(m->down);
+    cudaFree(m->d_h);
+    delete m;
+    return TLLM_OK;
+}
+
+int tllm_mlp_forward(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y, void* H, void* stream) {
+    if (!m || !X || !Y) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: NULL pointer");
+    if (rows <= 0) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: rows must be positive");
+    if (x_dtype != TLLM_F32 && x_dtype != TLLM_F16 && x_dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: unsupported dtype");
+    if (!H && rows > 16) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: pass H for more than 16 rows");
+    const size_t e = dtype_size(x_dtype);
+    char* h = (char*)(H ? H : m->d_h);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int mr = m->gate_up->max_rows;
+    for (int r0 = 0; r0 < rows; r0 += mr) {
+        const int mm = rows - r0 < mr ? rows - r0 : mr;
+        int rc = run_ts(m->gate_up, (const char*)X + (size_t)r0 * m->hidden * e, x_dtype, TLLM_ROW_MAJOR, m->hidden, mm,
+                        h + (size_t)r0 * m->inter * e, x_dtype, m->inter, 1, m->s_gate, m->s_up, st);
+        if (rc) return rc;
+        rc = run_ts(m->down, h + (size_t)r0 * m->inter * e, x_dtype, TLLM_ROW_MAJOR, m->inter, mm, (char*)Y + (size_t)r0 * m->hidden * e,
+                    x_dtype, m->hidden, 0, m->down->scale, 0.f, st);
+        if (rc) return rc;
+    }
+    return TLLM_OK;
+}
+
+int tllm_mlp_get_info(const tllm_mlp* m, tllm_weight_info* gate_up, tllm_weight_info* down) {
+    if (!m) return fail(TLLM_ERR_ARG, "tllm_mlp_get_info: NULL");
+    if (gate_up) tllm_weight_get_info(m->gate_up, gate_up);
+    if (down) tllm_weight_get_info(m->down, down);
+    return TLLM_OK;
+}
+
+int tllm_silu_mul(void* g, const void* u, int dtype, int64_t n, void* stream) {
+    if (!g || !u || n < 0) return fail(TLLM_ERR_ARG, "tllm_silu_mul: bad argument");
+    if (dtype != TLLM_F32 && dtype != TLLM_F16 && dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "tllm_silu_mul: unsupported dtype");
+    if (n == 0) return TLLM_OK;
+    silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(g, u, dtype, (long long)n);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return TLLM_OK;
+}
+
+}  // extern "C"

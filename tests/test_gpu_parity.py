@@ -1,0 +1,323 @@
+"""Parity of the CUDA path with the oracle -- every call goes through the C ABI (ctypes on libtllm.so).
+
+Bars: bit-exact wherever the arithmetic is exact (integer-valued fp32 / fp16 / bf16 activations as in the
+reference's own verify_* functions, main.cpp:1403; int8 activations with int32 accumulation); for N(0,1)
+activations  max|Y - Y_ref| <= 1e-3 * max|Y_ref|  with Y_ref the fp64 product of the activations as stored
+(the tolerance the task states for fp16/bf16 after reordering sums; fp32 accumulation lands near 1e-6).
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import random_ternary
+from ternaryllm_b200 import PackedMLP, PackedWeight, TernaryLinear, ter_spmm
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3
+DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch.device("cuda", 0)
+
+
+def int_acts(rng, M, K, lim, dtype):
+    x = rng.integers(-lim, lim + 1, size=(M, K)).astype(np.float64)
+    return x, torch.tensor(x, dtype=dtype, device=dev())
+
+
+def rel_err(y, ref):
+    return float(np.max(np.abs(y - ref)) / max(1e-30, np.max(np.abs(ref))))
+
+
+# ------------------------------------------------------------------------------------------------------
+# ter_spmm on the reference's arrays (golden fixtures from the reference's Python packer)
+# ------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("case", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_ter_spmm_on_golden_arrays(gpu_packers, case, dtype):
+    c = gpu_packers[case]
+    K, N = c["w"].shape
+    T = int(c["T"])
+    rng = np.random.default_rng(11)
+    ri = torch.tensor(c["mcsc_idx"].astype(np.int16), device=dev())
+    co = torch.tensor(c["mcsc_off"], device=dev())
+    til = torch.zeros(1, dtype=torch.int16, device=dev())
+    for B, M in ((1, 1), (2, 5), (3, 8)):
+        xs = rng.integers(-8, 9, size=(B, M, K)).astype(np.float64)
+        X = torch.tensor(xs, dtype=DT[dtype], device=dev())
+        Y = ter_spmm.ter_spmm(X, ri, co, til, B, M, N, K, False, False, tile_k=T)
+        assert Y.shape == (B, M, N) and Y.dtype == DT[dtype]
+        for b in range(B):
+            want = oracle.mcsc_product_f64(xs[b], c["mcsc_idx"], c["mcsc_off"], N, K, T)
+            assert np.array_equal(Y[b].double().cpu().numpy(), want)
+            assert np.array_equal(want, oracle.dense_f64(xs[b], c["w"]))
+        # the layout the reference kernel indexes: [K][M] per batch item
+        Xt = X.transpose(1, 2).contiguous()
+        if M != K:
+            Yt = ter_spmm.ter_spmm(Xt, ri, co, til, B, M, N, K, False, False, tile_k=T)
+            assert torch.equal(Yt, Y)
+    # scale and out=
+    out = torch.empty((1, 2, N), dtype=torch.float32, device=dev())
+    xs = rng.integers(-8, 9, size=(1, 2, K)).astype(np.float64)
+    ter_spmm.ter_spmm(torch.tensor(xs, dtype=torch.float32, device=dev()), ri, co, til, 1, 2, N, K, False, False, scale=0.5, out=out, tile_k=T)
+    assert np.array_equal(out[0].double().cpu().numpy(), oracle.dense_f64(xs[0], c["w"], 0.5))
+
+
+def test_ter_spmm_error_behaviour(gpu_packers):
+    c = gpu_packers["a"]
+    K, N = c["w"].shape
+    ri = torch.tensor(c["mcsc_idx"].astype(np.int16), device=dev())
+    co = torch.tensor(c["mcsc_off"], device=dev())
+    X = torch.zeros((1, 2, K), device=dev())
+    with pytest.raises(RuntimeError):
+        ter_spmm.ter_spmm(X.cpu(), ri, co, ri, 1, 2, N, K, False, False, tile_k=16)          # X not on CUDA
+    with pytest.raises(RuntimeError):
+        ter_spmm.ter_spmm(X, ri.int(), co, ri, 1, 2, N, K, False, False, tile_k=16)          # wrong index dtype
+    with pytest.raises(RuntimeError):
+        ter_spmm.ter_spmm(X, ri, co, ri, 1, 2, N, K, False, False, tile_k=32)                # offsets do not match TILE_K
+    # batch 0: nothing is launched and an empty [0, M, N] tensor comes back, as in the reference
+    Y0 = ter_spmm.ter_spmm(X[:0], ri, co, ri, 0, 2, N, K, False, False, tile_k=16)
+    assert Y0.shape == (0, 2, N)
+
+
+def test_ter_spmm_int8(gpu_packers):
+    c = gpu_packers["b"]
+    K, N = c["w"].shape
+    T = int(c["T"])
+    rng = np.random.default_rng(2)
+    x8 = rng.integers(-128, 128, size=(1, 7, K)).astype(np.int8)
+    ri = torch.tensor(c["mcsc_idx"].astype(np.int16), device=dev())
+    co = torch.tensor(c["mcsc_off"], device=dev())
+    Y = ter_spmm.ter_spmm(torch.tensor(x8, device=dev()), ri, co, ri, 1, 7, N, K, False, False, tile_k=T)
+    assert Y.dtype == torch.int32
+    assert np.array_equal(Y[0].cpu().numpy().astype(np.int64), oracle.dense_i64(x8[0], c["w"]))
+
+
+# ------------------------------------------------------------------------------------------------------
+# tile-stream kernel
+# ------------------------------------------------------------------------------------------------------
+SHAPES = [
+    # K, N, sparsity, pack options
+    (64, 8, 0.5, {}),
+    (1000, 70, 0.75, {}),
+    (2048, 256, 0.5, {}),
+    (1536, 130, 0.9, {}),
+    (4096, 344, 0.75, {}),
+    (3000, 2, 0.5, {}),
+    (700, 40, 0.7, {"tile_rows": 256}),
+    (700, 40, 0.7, {"tile_rows": 64, "lanes_per_list": 16}),
+    (700, 40, 0.0, {"num_ctas": 3}),                      # dense, several tiles per block
+    (2500, 64, 0.6, {"num_ctas": 2, "lanes_per_list": 1}),
+    (5000, 24, 0.8, {"num_ctas": 1}),                     # one block walks five tiles
+    (128, 16, 1.0, {}),                                   # all-zero weight
+]
+
+
+@pytest.mark.parametrize("K,N,s,opts", SHAPES)
+def test_tstream_bit_exact_on_integer_activations(K, N, s, opts):
+    rng = np.random.default_rng(K * 31 + N)
+    w = random_ternary(rng, K, N, s)
+    if N > 12:
+        w[:, 3] = 0
+        w[:, 9] = 1
+        w[:, 10] = -1
+    pw = PackedWeight.from_dense(w, scale=1.0, **opts)
+    for M in (1, 2, 3, 4, 5, 8, 13, 16, 17, 40):
+        xs, X = int_acts(rng, M, K, 512, torch.float32)      # |sum| < 2^24: exact in fp32, as in main.cpp:1403
+        want = oracle.dense_f64(xs, w)
+        Y = pw.matmul(X)
+        assert np.array_equal(Y.double().cpu().numpy(), want), (M,)
+        if M in (1, 4, 16):
+            Yc = pw.matmul(X.t().contiguous(), col_major=True)
+            assert torch.equal(Yc, Y)
+    for dtype, lim in (("f16", 1), ("bf16", 1)):
+        # +-1/0 activations keep every sum exactly representable in the narrow output type for small K
+        xs, X = int_acts(rng, 4, K, lim, DT[dtype])
+        want = oracle.round_to(oracle.dense_f64(xs, w), 1 if dtype == "f16" else 2)
+        assert np.array_equal(pw.matmul(X).double().cpu().numpy(), want)
+    x8 = rng.integers(-128, 128, size=(6, K)).astype(np.int8)
+    Y8 = pw.matmul(torch.tensor(x8, device=dev()))
+    assert Y8.dtype == torch.int32 and np.array_equal(Y8.cpu().numpy().astype(np.int64), oracle.dense_i64(x8, w))
+    pw.check()
+    pw.close()
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_tstream_tolerance_on_gaussian_activations(dtype, M):
+    rng = np.random.default_rng(M)
+    K, N, s = 4096, 688, 0.75
+    w = random_ternary(rng, K, N, s)
+    scale = float(np.float16(rng.uniform(0.01, 0.05)))
+    pw = PackedWeight.from_dense(w, scale=scale)
+    X = torch.tensor(rng.standard_normal((M, K)), dtype=DT[dtype], device=dev())
+    ref = oracle.dense_f64(X.double().cpu().numpy(), w, scale)          # activations as stored
+    Y = pw.matmul(X).double().cpu().numpy()
+    # the result is rounded once to the output dtype: allow that rounding on top of the stated tolerance
+    eps = {"f32": 2.0 ** -24, "f16": 2.0 ** -11, "bf16": 2.0 ** -8}[dtype]
+    assert rel_err(Y, ref) <= TOL * (1.0 if dtype == "f32" else 1.0) + eps
+    if dtype == "f32":
+        assert rel_err(Y, ref) < 1e-5
+    pw.close()
+
+
+def test_repeated_calls_and_scale_update():
+    rng = np.random.default_rng(3)
+    K, N = 2048, 512
+    w = random_ternary(rng, K, N, 0.6)
+    pw = PackedWeight.from_dense(w, scale=2.0)
+    xs, X = int_acts(rng, 4, K, 16, torch.float32)
+    want = oracle.dense_f64(xs, w, 2.0)
+    for _ in range(20):     # back to back on one stream: split-K counters must return to zero every time
+        Y = pw.matmul(X)
+    assert np.array_equal(Y.double().cpu().numpy(), want)
+    pw.set_scale(0.25)
+    assert np.array_equal(pw.matmul(X).double().cpu().numpy(), oracle.dense_f64(xs, w, 0.25))
+    info = pw.info
+    assert info["nnz"] == int((w != 0).sum()) and info["scratch_bytes"] > 0
+    pw.check()
+
+
+def test_host_buffer_entry_point():
+    rng = np.random.default_rng(4)
+    K, N = 1024, 96
+    w = random_ternary(rng, K, N, 0.5)
+    pw = PackedWeight.from_dense(w)
+    x = rng.integers(-512, 513, size=(8, K)).astype(np.float32)
+    want = oracle.dense_f64(x, w)
+    assert np.array_equal(pw.matmul_host(x).astype(np.float64), want)
+    # the col-major CPU kernels' convention: X [K][M] in, Y [N][M] out (GEMM_CPU_FP32.cpp:509-538)
+    yt = pw.matmul_host(np.ascontiguousarray(x.T), col_major=True, y_col_major=True)
+    assert np.array_equal(yt.T.astype(np.float64), want)
+    x8 = rng.integers(-10, 11, size=(64, K)).astype(np.int8)
+    y32 = pw.matmul_host(x8)
+    assert np.array_equal(y32.astype(np.int64), oracle.dense_i64(x8, w))
+    # the reference's int8 kernels wrap modulo 256 (GEMM_CPU_INT8.cpp:33-40): truncating the int32 result gives the same bytes
+    assert np.array_equal(y32.astype(np.int8), oracle.int8_wrap(x8, w))
+
+
+# ------------------------------------------------------------------------------------------------------
+# reference CPU formats in, reference CPU kernels' results out (golden fixture from the compiled reference)
+# ------------------------------------------------------------------------------------------------------
+def test_cpu_formats_reproduce_reference_kernel_outputs(cpu_reference):
+    import re
+
+    fx = cpu_reference
+    K, N = fx["W"].shape
+    X = np.ascontiguousarray(fx["X"])                       # [M][K] integer-valued fp32
+    XT = np.ascontiguousarray(X.T)
+    seen = {}
+    for name, fmt in zip(fx["kernel_names"], fx["kernel_formats"]):
+        if fmt in seen:
+            continue
+        if fmt == "merged":
+            pw = PackedWeight.from_cpu_format(1, 1, 0, fx["merged_meta"], fx["merged_ri"], N, K)
+            wname = "W"
+        elif fmt == "naive":
+            meta = np.concatenate([fx["sf_csn"], fx["sf_csp"]])
+            ri = np.concatenate([fx["sf_rin"], fx["sf_rip"]])
+            pw = PackedWeight.from_cpu_format(0, 1, 0, meta, ri, N, K, aux=len(fx["sf_rin"]))
+            wname = "W"
+        else:
+            m = re.match(r"grp\.(\w+)\.G(\d+)\.(\w+)\.i(\d)\.s(\d+)", fmt)
+            wname, G, method, inter, simd = m.group(1), int(m.group(2)), m.group(3), int(m.group(4)), int(m.group(5))
+            kind = {"min": 2, "mid": 3, "max": 4, "uniform": 5}[method]
+            chunk = 0 if inter else (simd if simd else G)
+            ri = fx[fmt + ".ri"]
+            if "GEMV" in name or "rowMajor" in name:
+                ri = ri.astype(np.int32)                     # the gather kernels take int32 ids (main.cpp:1446-1449)
+            pw = PackedWeight.from_cpu_format(kind, G, chunk, fx[fmt + ".meta"], ri, N, K)
+        seen[fmt] = True
+        want_col = fx[f"direct_col.{wname}"]                 # [N][M], what every reference kernel reproduced
+        got = pw.matmul_host(XT, col_major=True, y_col_major=True)
+        assert np.array_equal(got, want_col), (name, fmt)
+        pw.close()
+    assert len(seen) >= 20
+    # int8 family
+    for wname in ("W", "Wun"):
+        key = f"int8_col.{wname}"
+        if key in fx.files:
+            pw = PackedWeight.from_dense(fx[wname])
+            y = pw.matmul_host(np.ascontiguousarray(fx["X8"].T), col_major=True, y_col_major=True)
+            assert np.array_equal(y.astype(np.int8), fx[key])
+
+
+# ------------------------------------------------------------------------------------------------------
+# modules
+# ------------------------------------------------------------------------------------------------------
+def test_ternary_linear_module():
+    g = torch.Generator().manual_seed(0)
+    lin = TernaryLinear(512, 96, sparsity=0.7, bias=False, scale=0.5, generator=g)
+    w = lin.ternary_weight.numpy()
+    assert lin.w_row_indices.dtype == torch.int16 and lin.w_col_offsets.dtype == torch.int32
+    rng = np.random.default_rng(0)
+    xs = rng.integers(-16, 17, size=(2, 5, 512)).astype(np.float64)
+    X = torch.tensor(xs, dtype=torch.float32, device=dev())
+    Y = lin(X)
+    assert Y.shape == (2, 5, 96)
+    for b in range(2):
+        assert np.array_equal(Y[b].double().cpu().numpy(), oracle.dense_f64(xs[b], w, 0.5))
+    assert torch.equal(lin(X.transpose(1, 2).contiguous()), Y)          # (batch, K, rows) form
+    assert torch.equal(lin(X[0]), Y[0])                                  # 2-D input
+    # the reference-layout buffers feed ter_spmm and give the same numbers (scale passed explicitly)
+    lin = lin.to(dev())
+    Y2 = ter_spmm.ter_spmm(X, lin.w_row_indices, lin.w_col_offsets, lin.w_col_tile_indices, 2, 5, 96, 512, False, False, scale=0.5)
+    assert torch.equal(Y2, Y)
+    with pytest.raises(RuntimeError):
+        lin(X.cpu())
+    # uniform weights: balanced +1 / -1 in every 512-block of a column
+    lu = TernaryLinear(1024, 32, sparsity=0.75, uniform=True, bias=False, generator=g)
+    wu = lu.ternary_weight.numpy()
+    assert np.all((wu[:512] == 1).sum(0) == (wu[:512] == -1).sum(0)) and abs((wu == 0).mean() - 0.75) < 1e-3
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_fused_mlp(dtype):
+    rng = np.random.default_rng(9)
+    hidden, inter = 1024, 2752
+    wg, wu = random_ternary(rng, hidden, inter, 0.6), random_ternary(rng, hidden, inter, 0.6)
+    wd = random_ternary(rng, inter, hidden, 0.6)
+    sg, su, sd = (float(np.float16(v)) for v in rng.uniform(0.01, 0.05, 3))
+    mlp = PackedMLP(wg, wu, wd, sg, su, sd)
+    mode = {"f32": 3, "f16": 1, "bf16": 2}[dtype]
+    for M in (1, 8, 32):
+        X = torch.tensor(rng.standard_normal((M, hidden)), dtype=DT[dtype], device=dev())
+        ref = oracle.mlp_f64(X.double().cpu().numpy(), wg, wu, wd, sg, su, sd, h_round=mode)
+        Y = mlp.forward(X).double().cpu().numpy()
+        eps = {"f32": 2.0 ** -24, "f16": 2.0 ** -11, "bf16": 2.0 ** -8}[dtype]
+        # h is rounded to the activation dtype between the two products, exactly like the oracle does
+        assert rel_err(Y, ref) <= TOL + 4 * eps, (M, rel_err(Y, ref))
+    # exact check of the epilogue alone on values where SiLU is benign: x = 0 -> h = 0 -> y = 0
+    Z = torch.zeros((3, hidden), dtype=DT[dtype], device=dev())
+    assert not mlp.forward(Z).any()
+    mlp.close()
+
+
+# ------------------------------------------------------------------------------------------------------
+# full benchmark size: size-independent properties + a dense fp64 product on the device
+# ------------------------------------------------------------------------------------------------------
+def test_full_size_llama7b_up_projection():
+    rng = np.random.default_rng(0)
+    K, N = 4096, 11008
+    r = rng.integers(0, 256, size=(K, N), dtype=np.uint8)
+    w = np.zeros((K, N), np.int8)
+    w[(r >= 192) & (r < 224)] = -1
+    w[r >= 224] = 1                                        # 75 % zeros, +-1 equiprobable
+    pw = PackedWeight.from_dense(w, scale=1.0)
+    Wd = torch.tensor(w, device=dev()).double()
+    for M in (1, 4, 16):
+        xs, X = int_acts(rng, M, K, 64, torch.float32)
+        Y = pw.matmul(X)
+        assert torch.equal(Y.double(), X.double() @ Wd)                  # exact: integer sums below 2^24
+        # linearity: (a+b) W = aW + bW  (exact on integers)
+        xs2, X2 = int_acts(rng, M, K, 64, torch.float32)
+        assert torch.equal(pw.matmul(X + X2), Y + pw.matmul(X2))
+    Xg = torch.tensor(rng.standard_normal((1, K)), dtype=torch.float16, device=dev())
+    Yg = pw.matmul(Xg).double()
+    ref = Xg.double() @ Wd
+    assert float((Yg - ref).abs().max() / ref.abs().max()) <= TOL + 2.0 ** -11
+    pw.check()
