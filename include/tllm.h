@@ -101,7 +101,8 @@ typedef struct tllm_pack_opts {
     int num_ctas;         /* thread blocks to schedule for; 0 = number of SMs of the current device */
     int lanes_per_list;   /* lanes that share one index list (power of two, 1..16); 0 = choose from density */
     int max_rows;         /* largest M a single call may pass (scratch is sized for it); 0 = 16 */
-    int reserved[4];
+    int k_splits;         /* thread blocks that share one column block along K; 0 = choose (1 = no split-K scratch) */
+    int reserved[3];
 } tllm_pack_opts;
 
 typedef struct tllm_weight_info {
@@ -146,6 +147,12 @@ int tllm_weight_set_scale(tllm_weight* w, float scale);
  * a kernel gave up on one of its bounded waits since the last check -- its output is then undefined --
  * and clears the condition. */
 int tllm_weight_check(tllm_weight* w);
+
+/* Diagnostics: while `device_buffer` (num_ctas*8 int64 in device memory) is set, every launch on this handle
+ * records per thread block the GPU global timer (ns) at: 0 start, 1 ordered behind the previous kernel, 2 list
+ * table arrived, 3 first activation table filled, 4 all lists consumed, 5 split-K arrival done, 6 end,
+ * 7 last bulk copy issued.  NULL switches it off (the default). */
+int tllm_weight_set_trace(tllm_weight* w, void* device_buffer);
 
 /* Y[rows][columns] = X . W . s   on device pointers, launched on `stream`.  rows <= max_rows of the
  * handle per launch; larger row counts are processed in chunks.  Calls on one handle must not overlap

@@ -18,7 +18,7 @@ ROW_MAJOR, COL_MAJOR = 0, 1
 
 class PackOpts(C.Structure):
     _fields_ = [("tile_rows", C.c_int), ("num_ctas", C.c_int), ("lanes_per_list", C.c_int), ("max_rows", C.c_int),
-                ("reserved", C.c_int * 4)]
+                ("k_splits", C.c_int), ("reserved", C.c_int * 3)]
 
 
 class WeightInfo(C.Structure):
@@ -51,6 +51,7 @@ SIGNATURES = {
     "tllm_weight_get_info": (_I, [_P, _P]),
     "tllm_weight_set_scale": (_I, [_P, _F]),
     "tllm_weight_check": (_I, [_P]),
+    "tllm_weight_set_trace": (_I, [_P, _P]),
     "tllm_spmm": (_I, [_P, _P, _I, _I, _I, _P, _I, _P]),
     "tllm_spmm_host": (_I, [_P, _P, _I, _I, _I, _P, _I, _I]),
     "tllm_mlp_create": (_I, [_P, _P, _P, _I, _I, _F, _F, _F, _P, _P]),

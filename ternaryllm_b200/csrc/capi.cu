@@ -60,7 +60,7 @@ struct tllm_weight {
     int device = 0;
     int max_rows = 16;
     uint4* d_stream = nullptr;
-    uint32_t* d_vstart = nullptr;
+    uint32_t* d_meta = nullptr;
     void* d_partial = nullptr;
     unsigned int* d_counters = nullptr;
     int* d_status = nullptr;
@@ -71,6 +71,7 @@ struct tllm_weight {
     void* h_pin = nullptr;
     size_t x_cap = 0, y_cap = 0, pin_cap = 0;
     cudaStream_t own_stream = nullptr;
+    long long* d_trace = nullptr;   // diagnostics: see tllm_weight_set_trace
 };
 
 struct tllm_mlp {
@@ -84,9 +85,9 @@ struct tllm_mlp {
 
 namespace {
 
-template <typename ACC, int MP, int NW>
+template <typename ACC, int MP, int NW, int D>
 int launch_ts(const TsParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = tstream_spmm_kernel<ACC, MP, NW>;
+    auto kern = tstream_spmm_kernel<ACC, MP, NW, D>;
     static std::mutex mu;
     static bool configured[64] = {};
     int dev = 0;
@@ -100,7 +101,7 @@ int launch_ts(const TsParams& p, int grid, size_t smem, cudaStream_t st) {
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3((NW + 1) * 32);
+    cfg.blockDim = dim3(NW * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute at[1];
@@ -115,11 +116,13 @@ int launch_ts(const TsParams& p, int grid, size_t smem, cudaStream_t st) {
 
 template <typename ACC>
 int dispatch_ts(const TsParams& p, int grid, size_t smem, cudaStream_t st) {
-    if (p.M <= 1) return launch_ts<ACC, 1, 31>(p, grid, smem, st);
-    if (p.M <= 2) return launch_ts<ACC, 2, 31>(p, grid, smem, st);
-    if (p.M <= 4) return launch_ts<ACC, 4, 31>(p, grid, smem, st);
-    if (p.M <= 8) return launch_ts<ACC, 8, 15>(p, grid, smem, st);
-    return launch_ts<ACC, 16, 15>(p, grid, smem, st);
+    // rows are padded to 1, 2, 4, 8 or 16; up to four rows run 24 warps with two batches of four index vectors
+    // per lane, wider tiles trade warps and batch size for registers
+    if (p.M <= 1) return launch_ts<ACC, 1, 24, 4>(p, grid, smem, st);
+    if (p.M <= 2) return launch_ts<ACC, 2, 24, 4>(p, grid, smem, st);
+    if (p.M <= 4) return launch_ts<ACC, 4, 24, 4>(p, grid, smem, st);
+    if (p.M <= 8) return launch_ts<ACC, 8, 16, 2>(p, grid, smem, st);
+    return launch_ts<ACC, 16, 16, 2>(p, grid, smem, st);
 }
 
 int check_types(int x_dtype, int y_dtype, const char* who) {
@@ -138,7 +141,7 @@ int run_ts(tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, i
     const TsLayout& L = w->lay;
     TsParams p{};
     p.stream = w->d_stream;
-    p.vstart = w->d_vstart;
+    p.meta = w->d_meta;
     p.X = X;
     p.Y = Y;
     p.partial = w->d_partial;
@@ -154,21 +157,25 @@ int run_ts(tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, i
     p.tiles = L.tiles;
     p.col_blocks = L.col_blocks;
     p.cols_per_block = L.cols_per_block;
+    p.sub_cols = L.sub_cols;
     p.k_splits = L.k_splits;
     p.tiles_per_cta = L.tiles_per_cta;
     int lg = 0;
     while ((1 << lg) < L.lanes_per_list) ++lg;
     p.lpl_log2 = lg;
-    p.nstages = TS_MAX_STAGES;
     p.epilogue = epilogue;
     p.y_ld = y_ld;
     p.x_ld = x_ld;
     p.scale = scale;
     p.scale2 = scale2;
+    p.trace = w->d_trace;
     std::memcpy(p.cta, L.cta, sizeof(TsCtaDesc) * (size_t)L.num_ctas);
-    const TsSmem sm = ts_smem_layout(TS_MAX_TILE_ROWS, TS_MAX_STAGES, TS_MAX_META_BYTES);
-    if (x_dtype == TLLM_I8) return dispatch_ts<int>(p, L.num_ctas, sm.total, st);
-    return dispatch_ts<float>(p, L.num_ctas, sm.total, st);
+    // bulk-copy staging of the activation tile needs every row segment to start and end on 16 bytes
+    const size_t e = dtype_size(x_dtype);
+    p.x_tma = x_layout == TLLM_ROW_MAJOR && ((uintptr_t)X % 16 == 0) && ((size_t)x_ld * e % 16 == 0) && ((size_t)L.tile_rows * e % 16 == 0) &&
+              ((size_t)L.inners * e % 16 == 0);
+    if (x_dtype == TLLM_I8) return dispatch_ts<int>(p, L.num_ctas, TS_SMEM_TOTAL, st);
+    return dispatch_ts<float>(p, L.num_ctas, TS_SMEM_TOTAL, st);
 }
 
 int upload(tllm_weight* w, const TsHostImage& img, float scale, int max_rows) {
@@ -176,14 +183,12 @@ int upload(tllm_weight* w, const TsHostImage& img, float scale, int max_rows) {
     w->scale = scale;
     w->max_rows = max_rows;
     CU_TRY(cudaGetDevice(&w->device));
-    // one stage of slack behind the stream: the last bulk copy of a block never reads past its own range,
-    // but keeping the allocation a multiple of a stage makes that independent of packer details
     w->stream_bytes = img.stream.size() * sizeof(uint16_t);
-    w->meta_bytes = img.vstart.size() * sizeof(uint32_t);
-    CU_TRY(cudaMalloc(&w->d_stream, w->stream_bytes + TS_STAGE_VECS * 16));
-    CU_TRY(cudaMalloc(&w->d_vstart, w->meta_bytes + 16));
+    w->meta_bytes = img.meta.size() * sizeof(uint32_t);
+    CU_TRY(cudaMalloc(&w->d_stream, w->stream_bytes + 512));
+    CU_TRY(cudaMalloc(&w->d_meta, w->meta_bytes + 16));
     CU_TRY(cudaMemcpy(w->d_stream, img.stream.data(), w->stream_bytes, cudaMemcpyHostToDevice));
-    CU_TRY(cudaMemcpy(w->d_vstart, img.vstart.data(), w->meta_bytes, cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemcpy(w->d_meta, img.meta.data(), w->meta_bytes, cudaMemcpyHostToDevice));
     const size_t partial_bytes = (size_t)img.lay.k_splits * max_rows * img.lay.columns * 4;
     const size_t counter_bytes = (size_t)img.lay.col_blocks * sizeof(unsigned int);
     w->scratch_bytes = partial_bytes + counter_bytes + sizeof(int);
@@ -204,9 +209,8 @@ int create_from_dense(const int8_t* dense, int inners, int columns, float scale,
     CU_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     int max_smem = 0;
     CU_TRY(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    const TsSmem sm = ts_smem_layout(TS_MAX_TILE_ROWS, TS_MAX_STAGES, TS_MAX_META_BYTES);
-    if ((int)sm.total > max_smem)
-        return fail(TLLM_ERR_ARG, "this device offers %d bytes of shared memory per block; the kernel needs %u (built for sm_100a)", max_smem, sm.total);
+    if ((int)TS_SMEM_TOTAL > max_smem)
+        return fail(TLLM_ERR_ARG, "this device offers %d bytes of shared memory per block; the kernel needs %u (built for sm_100a)", max_smem, (unsigned)TS_SMEM_TOTAL);
     TsHostImage img;
     if (sms > TS_MAX_CTAS) sms = TS_MAX_CTAS;
     const char* msg = ts_pack_dense(dense, inners, columns, opts, sms, &img);
@@ -252,11 +256,11 @@ int tllm_ter_spmm(const void* X, int x_dtype, int x_layout, const int16_t* row_i
     (void)col_tile_idx;
     (void)uniformed;
     (void)padded;
+    if (batch == 0) return TLLM_OK;   // the reference launches nothing for a 2-D input (TernaryLinear.py:168)
     if (!X || !row_idx || !col_off || !Y) return fail(TLLM_ERR_ARG, "tllm_ter_spmm: NULL pointer");
     if (batch < 0 || rows <= 0 || columns <= 0 || inners <= 0 || tile_k <= 0) return fail(TLLM_ERR_ARG, "tllm_ter_spmm: bad shape");
     const int rc = check_types(x_dtype, y_dtype, "tllm_ter_spmm");
     if (rc) return rc;
-    if (batch == 0) return TLLM_OK;   // the reference launches nothing for a 2-D input (TernaryLinear.py:168)
     if (batch > 65535) return fail(TLLM_ERR_ARG, "tllm_ter_spmm: batch too large");
     constexpr int MC = 4;
     dim3 grid((columns + 7) / 8, (rows + MC - 1) / MC, batch), block(256);
@@ -300,7 +304,7 @@ int tllm_weight_create_cpu_format(int kind, int group, int chunk, const int32_t*
 int tllm_weight_destroy(tllm_weight* w) {
     if (!w) return TLLM_OK;
     cudaFree(w->d_stream);
-    cudaFree(w->d_vstart);
+    cudaFree(w->d_meta);
     cudaFree(w->d_partial);
     cudaFree(w->d_counters);
     cudaFree(w->d_status);
@@ -340,6 +344,12 @@ int tllm_weight_set_scale(tllm_weight* w, float scale) {
     return TLLM_OK;
 }
 
+int tllm_weight_set_trace(tllm_weight* w, void* device_buffer) {
+    if (!w) return fail(TLLM_ERR_ARG, "tllm_weight_set_trace: NULL");
+    w->d_trace = (long long*)device_buffer;
+    return TLLM_OK;
+}
+
 int tllm_weight_check(tllm_weight* w) {
     if (!w) return fail(TLLM_ERR_ARG, "tllm_weight_check: NULL");
     int st = 0;
@@ -348,7 +358,7 @@ int tllm_weight_check(tllm_weight* w) {
         cudaMemset(w->d_status, 0, sizeof(int));
         cudaMemset(w->d_counters, 0, (size_t)w->lay.col_blocks * sizeof(unsigned int));
         return fail(TLLM_ERR_KERNEL, "a bounded wait ran out inside the kernel (code %d: %s)", st,
-                    st == TS_ERR_FULL_WAIT ? "index stream stage never arrived" : st == TS_ERR_EMPTY_WAIT ? "ring stage never released" : "list table never arrived");
+                    st == TS_ERR_X_WAIT ? "activation tile never arrived" : "unit table never arrived");
     }
     return TLLM_OK;
 }

@@ -54,6 +54,10 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+// hint: bring [p, p+bytes) into L2 (16-byte aligned, size a multiple of 16); nothing waits on it
+__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void named_bar(int id, int threads) {
@@ -86,6 +90,18 @@ __device__ __forceinline__ float load_act_f32(const void* X, int dtype, size_t i
     }
 }
 __device__ __forceinline__ int load_act_i32(const void* X, int dtype, size_t i) { return (int)__ldg((const int8_t*)X + i); }
+// Same through L2 only (ld.global.cg): used where the activations may have been written by the kernel that
+// precedes this one in the stream while this one was already resident (programmatic dependent launch), so
+// that no line cached in an SM's L1 before griddepcontrol.wait can be served.
+__device__ __forceinline__ float load_act_f32_cg(const void* X, int dtype, size_t i) {
+    switch (dtype) {
+        case TLLM_F32: return __ldcg((const float*)X + i);
+        case TLLM_F16: return __half2float(__ushort_as_half(__ldcg((const unsigned short*)X + i)));
+        case TLLM_BF16: return __bfloat162float(__ushort_as_bfloat16(__ldcg((const unsigned short*)X + i)));
+        default: return (float)__ldcg((const signed char*)X + i);
+    }
+}
+__device__ __forceinline__ int load_act_i32_cg(const void* X, int dtype, size_t i) { return (int)__ldcg((const signed char*)X + i); }
 
 __device__ __forceinline__ void store_out(void* Y, int dtype, size_t i, float v) {
     switch (dtype) {
@@ -104,93 +120,146 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return g * u / (1.
 // ---------------------------------------------------------------------------------------------------
 struct TsParams {
     const uint4* stream;
-    const uint32_t* vstart;
+    const uint32_t* meta;
     const void* X;
     void* Y;
     void* partial;            // [k_splits][M][columns] fp32 / int32
     unsigned int* counters;   // [col_blocks], zero between launches
     int* status;              // 0, or an error code written by a block whose bounded wait ran out
+    long long* trace;         // optional: 8 globaltimer stamps per block (diagnostics), or nullptr
     int x_dtype, x_layout, y_dtype;
     int M;                    // rows in this launch (<= MP)
     int K, N, T, tiles;
-    int col_blocks, cols_per_block, k_splits, tiles_per_cta;
-    int lpl_log2, nstages;
+    int col_blocks, cols_per_block, sub_cols, k_splits, tiles_per_cta;
+    int lpl_log2;
     int epilogue;             // 0: Y = acc*scale ; 1: columns are (gate,up) pairs, Y[c/2] = silu(g*scale)*(u*scale2)
     int y_ld;                 // row stride of Y in elements
     int x_ld;                 // row-major X: elements between rows (K); column-major X: elements between k (total rows)
+    int x_tma;                // 1: X is row-major and 16-byte aligned row by row, so tiles of it can be staged by bulk copies
     float scale, scale2;
     TsCtaDesc cta[TS_MAX_CTAS];
 };
 
-#define TS_ERR_FULL_WAIT 101
-#define TS_ERR_EMPTY_WAIT 102
-#define TS_ERR_META_WAIT 103
-
-// shared-memory carve-up (bytes from a 128-byte aligned base)
-struct TsSmem {
-    uint32_t table, ring, meta, bars, total;
-};
-__host__ __device__ inline TsSmem ts_smem_layout(int T, int nstages, int meta_bytes) {
-    TsSmem s;
-    s.table = 0;
-    s.ring = (uint32_t)(T + 1) * 128u;
-    s.meta = s.ring + (uint32_t)nstages * TS_STAGE_VECS * 16u;
-    s.bars = s.meta + (((uint32_t)meta_bytes + 127u) & ~127u);
-    s.total = s.bars + 256u;
-    return s;
+__device__ __forceinline__ long long global_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
 }
+#define TS_STAMP(slot)                                                                       \
+    do {                                                                                     \
+        if (p.trace && tid == 0) p.trace[(size_t)cta * 8 + (slot)] = global_ns();            \
+    } while (0)
+
+#define TS_L2_PREFETCH_BYTES (512u * 1024u)   // per block, at kernel start
+#define TS_ERR_META_WAIT 103
+#define TS_ERR_X_WAIT 104
+
+// shared-memory carve-up (bytes from a 128-byte aligned base); the same for every launch
+#define TS_SMEM_TABLE 0u
+#define TS_SMEM_ACC (((TS_MAX_TILE_ROWS + 1) * 128u + 127u) & ~127u)
+#define TS_SMEM_STAGE (TS_SMEM_ACC + 16u * TS_MAX_SUB_COLS * 4u)
+#define TS_SMEM_META (TS_SMEM_STAGE + TS_STAGE_BYTES)
+#define TS_SMEM_BARS (TS_SMEM_META + TS_MAX_META_BYTES)
+#define TS_SMEM_TOTAL (TS_SMEM_BARS + 128u)
+
+template <typename T>
+__device__ __forceinline__ T bits_as(uint32_t v);
+template <>
+__device__ __forceinline__ float bits_as<float>(uint32_t v) { return __uint_as_float(v); }
+template <>
+__device__ __forceinline__ int bits_as<int>(uint32_t v) { return (int)v; }
 
 // One gather of the lane's slice of table row `id`: EB bytes = MP accumulators' worth of activations.
 // The table row is 128 bytes = 8 chunks of 16 bytes holding 128/EB copies of the entry; each lane reads
 // the copy (and, for entries wider than 16 bytes, the chunk rotation) that makes the 8 lanes of every
-// quarter-warp hit 8 different 16-byte bank groups.
+// quarter-warp hit 8 different 16-byte bank groups, whatever rows they ask for.  All address arithmetic is
+// 32-bit element indexing from a lane-specific shared-memory base: one multiply-add per row id.
 template <typename ACC, int MP>
 struct Gatherer {
     static constexpr int EB = 4 * MP;
     static constexpr int NCH = EB >= 16 ? EB / 16 : 1;
-    uint32_t off[NCH];   // byte offset inside the 128-byte row for each of the NCH loads
+    struct alignas(8) P2 {
+        ACC a, b;
+    };
+    struct alignas(16) P4 {
+        ACC a, b, c, d;
+    };
+    uint32_t a1;         // shared-memory byte address of this lane's copy (EB == 4: 4-byte entries, 32 copies)
+    uint32_t a2;         // EB == 8 : 8-byte entries, 16 copies
+    uint32_t a4[NCH];    // EB >= 16: this lane's copy, chunks in rotated order
     int rot;
 
-    __device__ __forceinline__ void init(int lane) {
-        if (EB == 4) {
-            off[0] = (lane & 31) * 4;
-            rot = 0;
-        } else if (EB == 8) {
-            off[0] = (lane & 15) * 8;
-            rot = 0;
-        } else {
-            const int l8 = lane & 7;
-            const int copy = l8 / NCH;
-            rot = l8 % NCH;
+    __device__ __forceinline__ void init(const unsigned char* table, int lane) {
+        const uint32_t t = smem_u32(table);
+        a1 = t + (uint32_t)(lane & 31) * 4u;
+        a2 = t + (uint32_t)(lane & 15) * 8u;
+        const int l8 = lane & 7;
+        const int copy = l8 / NCH;
+        rot = EB >= 16 ? l8 % NCH : 0;
 #pragma unroll
-            for (int j = 0; j < NCH; ++j) off[j] = (uint32_t)((copy * NCH + ((rot + j) % NCH)) * 16);
-        }
+        for (int j = 0; j < NCH; ++j) a4[j] = t + (uint32_t)(EB >= 16 ? copy * NCH + ((rot + j) % NCH) : 0) * 16u;
     }
-    // acc += sign-free table[id]; accumulators stay in "rotated" chunk order until unrotate()
-    __device__ __forceinline__ void add(const unsigned char* table, uint32_t id, ACC (&acc)[MP]) const {
-        const unsigned char* row = table + (size_t)id * 128u;
+    // explicit 32-bit shared-memory loads: one multiply-add per row id, no generic-pointer arithmetic
+    static __device__ __forceinline__ ACC lds1(uint32_t a) {
+        uint32_t v;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a));
+        return bits_as<ACC>(v);
+    }
+    static __device__ __forceinline__ P2 lds2(uint32_t a) {
+        uint32_t x, y;
+        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(x), "=r"(y) : "r"(a));
+        P2 r;
+        r.a = bits_as<ACC>(x);
+        r.b = bits_as<ACC>(y);
+        return r;
+    }
+    static __device__ __forceinline__ P4 lds4(uint32_t a) {
+        uint32_t x, y, z, w;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x), "=r"(y), "=r"(z), "=r"(w) : "r"(a));
+        P4 r;
+        r.a = bits_as<ACC>(x);
+        r.b = bits_as<ACC>(y);
+        r.c = bits_as<ACC>(z);
+        r.d = bits_as<ACC>(w);
+        return r;
+    }
+    // acc += table[id]; accumulators stay in "rotated" chunk order until unrotate()
+    __device__ __forceinline__ void add(uint32_t id, ACC (&acc)[MP]) const {
         if (EB == 4) {
-            acc[0] += *(const ACC*)(row + off[0]);
+            acc[0] += lds1(a1 + id * 128u);
         } else if (EB == 8) {
-            struct alignas(8) P2 {
-                ACC a, b;
-            };
-            const P2 v = *(const P2*)(row + off[0]);
+            const P2 v = lds2(a2 + id * 128u);
             acc[0] += v.a;
-            acc[1] += v.b;
+            acc[1 % MP] += v.b;
         } else {
 #pragma unroll
             for (int j = 0; j < NCH; ++j) {
-                struct alignas(16) P4 {
-                    ACC a, b, c, d;
-                };
-                const P4 v = *(const P4*)(row + off[j]);
-                acc[4 * j + 0] += v.a;
-                acc[4 * j + 1] += v.b;
-                acc[4 * j + 2] += v.c;
-                acc[4 * j + 3] += v.d;
+                const P4 v = lds4(a4[j] + id * 128u);
+                acc[(4 * j + 0) % MP] += v.a;
+                acc[(4 * j + 1) % MP] += v.b;
+                acc[(4 * j + 2) % MP] += v.c;
+                acc[(4 * j + 3) % MP] += v.d;
             }
         }
+    }
+    __device__ __forceinline__ void add8(const uint4& q, ACC (&acc)[MP]) const {
+        if (EB == 4) {
+            // one accumulator: add the eight gathered values as a tree (depth 4) instead of a chain of 8
+            const ACC v0 = lds1(a1 + (q.x & 0xffffu) * 128u), v1 = lds1(a1 + (q.x >> 16) * 128u);
+            const ACC v2 = lds1(a1 + (q.y & 0xffffu) * 128u), v3 = lds1(a1 + (q.y >> 16) * 128u);
+            const ACC v4 = lds1(a1 + (q.z & 0xffffu) * 128u), v5 = lds1(a1 + (q.z >> 16) * 128u);
+            const ACC v6 = lds1(a1 + (q.w & 0xffffu) * 128u), v7 = lds1(a1 + (q.w >> 16) * 128u);
+            acc[0] += ((v0 + v1) + (v2 + v3)) + ((v4 + v5) + (v6 + v7));
+            return;
+        }
+        add(q.x & 0xffffu, acc);
+        add(q.x >> 16, acc);
+        add(q.y & 0xffffu, acc);
+        add(q.y >> 16, acc);
+        add(q.z & 0xffffu, acc);
+        add(q.z >> 16, acc);
+        add(q.w & 0xffffu, acc);
+        add(q.w >> 16, acc);
     }
     // bring the accumulators back to row order: slot j holds chunk (rot + j) % NCH
     __device__ __forceinline__ void unrotate(ACC (&acc)[MP]) const {
@@ -199,8 +268,8 @@ struct Gatherer {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const ACC t = acc[i];
-                    acc[i] = acc[4 + i];
-                    acc[4 + i] = t;
+                    acc[i] = acc[(4 + i) % MP];
+                    acc[(4 + i) % MP] = t;
                 }
             }
         } else if (NCH == 4) {
@@ -211,7 +280,7 @@ struct Gatherer {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[4 * ((j + 1) % 4) + i] = t[4 * j + i];
+                    for (int i = 0; i < 4; ++i) acc[(4 * ((j + 1) % 4) + i) % MP] = t[(4 * j + i) % MP];
 #pragma unroll
                 for (int i = 0; i < MP; ++i) t[i] = acc[i];
             }
@@ -219,7 +288,7 @@ struct Gatherer {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[4 * ((j + 2) % 4) + i] = t[4 * j + i];
+                    for (int i = 0; i < 4; ++i) acc[(4 * ((j + 2) % 4) + i) % MP] = t[(4 * j + i) % MP];
             }
         }
     }
@@ -231,240 +300,388 @@ template <>
 __device__ __forceinline__ float load_act<float>(const void* X, int dtype, size_t i) { return load_act_f32(X, dtype, i); }
 template <>
 __device__ __forceinline__ int load_act<int>(const void* X, int dtype, size_t i) { return load_act_i32(X, dtype, i); }
+template <typename ACC>
+__device__ __forceinline__ ACC load_act_cg(const void* X, int dtype, size_t i);
+template <>
+__device__ __forceinline__ float load_act_cg<float>(const void* X, int dtype, size_t i) { return load_act_f32_cg(X, dtype, i); }
+template <>
+__device__ __forceinline__ int load_act_cg<int>(const void* X, int dtype, size_t i) { return load_act_i32_cg(X, dtype, i); }
 
-// NW consumer warps + 1 producer warp.
-template <typename ACC, int MP, int NW>
-__global__ void __launch_bounds__((NW + 1) * 32, 1) tstream_spmm_kernel(const __grid_constant__ TsParams p) {
+// activation element i of a staged (shared-memory) tile
+template <typename ACC>
+__device__ __forceinline__ ACC staged_act(const unsigned char* st, int dtype, uint32_t i);
+template <>
+__device__ __forceinline__ float staged_act<float>(const unsigned char* st, int dtype, uint32_t i) {
+    switch (dtype) {
+        case TLLM_F32: return ((const float*)st)[i];
+        case TLLM_F16: return __half2float(((const __half*)st)[i]);
+        case TLLM_BF16: return __bfloat162float(((const __nv_bfloat16*)st)[i]);
+        default: return (float)((const signed char*)st)[i];
+    }
+}
+template <>
+__device__ __forceinline__ int staged_act<int>(const unsigned char* st, int dtype, uint32_t i) { return (int)((const signed char*)st)[i]; }
+
+__device__ __forceinline__ uint32_t act_bytes(int dtype) { return dtype == TLLM_F32 ? 4u : (dtype == TLLM_I8 ? 1u : 2u); }
+
+// Writes table row k (128 bytes: 128/EB copies of the MP activations of matrix row k) from val[0..MP).
+template <typename ACC, int MP>
+__device__ __forceinline__ void fill_row(unsigned char* table, int k, int lane, const ACC (&val)[MP]) {
+    constexpr int EB = 4 * MP;
+    constexpr int NCH = EB >= 16 ? EB / 16 : 1;
+    struct alignas(16) P4 {
+        ACC a, b, c, d;
+    };
+    P4* row = (P4*)(table + (size_t)k * 128u);
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+        const int c = (jj + lane) & 7;   // chunk written in this round
+        P4 v;
+        if (EB == 4) {
+            v.a = v.b = v.c = v.d = val[0];
+        } else if (EB == 8) {
+            v.a = v.c = val[0];
+            v.b = v.d = val[1 % MP];
+        } else {
+            // chunk c holds rows 4*(c % NCH) .. +3
+            const int h = c % NCH;
+            v.a = val[0];
+            v.b = val[1 % MP];
+            v.c = val[2 % MP];
+            v.d = val[3 % MP];
+#pragma unroll
+            for (int t = 1; t < NCH; ++t)
+                if (h == t) {
+                    v.a = val[(4 * t + 0) % MP];
+                    v.b = val[(4 * t + 1) % MP];
+                    v.c = val[(4 * t + 2) % MP];
+                    v.d = val[(4 * t + 3) % MP];
+                }
+        }
+        row[c] = v;
+    }
+}
+
+// NW warps, all of them consumers; D index vectors in flight per lane.
+template <typename ACC, int MP, int NW, int D>
+__global__ void __launch_bounds__(NW * 32, 1) tstream_spmm_kernel(const __grid_constant__ TsParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int EB = 4 * MP;
     constexpr int NCH = EB >= 16 ? EB / 16 : 1;
-    constexpr int CT = NW * 32;   // consumer threads
+    constexpr int NT = NW * 32;
+    constexpr int NV = EB == 4 ? 1 : (EB == 8 ? 2 : 4);   // activations per 16-byte table slot
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x;
     const int b = cta % p.col_blocks, j = cta / p.col_blocks;
     const TsCtaDesc d = p.cta[cta];
-    const TsSmem sm = ts_smem_layout(p.T, p.nstages, TS_MAX_META_BYTES);
 
-    unsigned char* table = smem + sm.table;
-    const uint4* ring = (const uint4*)(smem + sm.ring);
-    const uint32_t* meta = (const uint32_t*)(smem + sm.meta);
-    uint64_t* bars = (uint64_t*)(smem + sm.bars);           // [0..7] full, [8..15] empty, [16] meta
-    volatile int* flags = (volatile int*)(bars + 20);       // [0] abort, [1] last-block flag
-    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + 8), bar_meta = smem_u32(bars + 16);
+    unsigned char* table = smem + TS_SMEM_TABLE;
+    ACC* acc_s = (ACC*)(smem + TS_SMEM_ACC);                   // [MP][sub_cols]
+    unsigned char* stage = smem + TS_SMEM_STAGE;
+    const uint32_t* meta = (const uint32_t*)(smem + TS_SMEM_META);
+    uint64_t* bars = (uint64_t*)(smem + TS_SMEM_BARS);         // [0] unit table arrived, [1] activation chunk arrived
+    volatile int* flags = (volatile int*)(bars + 4);           // [0] abort, [1] last-block flag, [2] next group of the wave
+    const uint32_t bar_meta = smem_u32(bars), bar_x = smem_u32(bars + 1);
 
     if (tid == 0) {
-        for (int s = 0; s < p.nstages; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, TS_STAGE_VECS);
-        }
         mbar_init(bar_meta, 1);
+        mbar_init(bar_x, 1);
         flags[0] = 0;
         flags[1] = 0;
+        flags[2] = NW;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
-    // Let the next kernel in the stream start as SMs drain; it will not touch anything this kernel writes
-    // before its own griddepcontrol.wait.
+    TS_STAMP(0);
+    // Let the next kernel in the stream start as SMs drain; nothing it does before its own
+    // griddepcontrol.wait touches what this kernel writes.
     pdl_launch_dependents();
-
-    const uint32_t nchunks = (d.nvec + TS_STAGE_VECS - 1) / TS_STAGE_VECS;
-
-    if (warp == NW) {
-        // ------------------------------ producer: weights only, no dependence on earlier kernels ------
-        if (lane == 0) {
-            mbar_expect_tx(bar_meta, d.meta_words * 4u);
-            bulk_g2s(smem_u32(smem + sm.meta), p.vstart + d.meta_off, d.meta_words * 4u, bar_meta);
-            uint32_t issued = 0;
-            bool ok = true;
-            for (uint32_t i = 0; i < nchunks && ok; ++i) {
-                const uint32_t s = i % (uint32_t)p.nstages, g = i / (uint32_t)p.nstages;
-                if (g >= 1) ok = bounded_wait(bar_empty + 8 * s, (g - 1) & 1, flags);
-                if (!ok) break;
-                const uint32_t vecs = min((uint32_t)TS_STAGE_VECS, d.nvec - i * TS_STAGE_VECS);
-                mbar_expect_tx(bar_full + 8 * s, vecs * 16u);
-                bulk_g2s(smem_u32(smem + sm.ring) + s * (TS_STAGE_VECS * 16u), p.stream + (size_t)d.stream_off + (size_t)i * TS_STAGE_VECS,
-                         vecs * 16u, bar_full + 8 * s);
-                issued = i + 1;
-            }
-            if (!ok) {
-                atomicExch(p.status, TS_ERR_EMPTY_WAIT);
-                // do not leave the block while copies that were issued may still land in its shared memory
-                const uint32_t first = issued > (uint32_t)p.nstages ? issued - (uint32_t)p.nstages : 0;
-                for (uint32_t i = first; i < issued; ++i) {
-                    const uint32_t s = i % (uint32_t)p.nstages, g = i / (uint32_t)p.nstages;
-                    const long long t0 = clock64();
-                    while (!mbar_try_wait(bar_full + 8 * s, g & 1) && clock64() - t0 < TLLM_WAIT_LIMIT_CLOCKS) {
-                    }
-                }
-            }
-        }
-        return;
+    if (tid == 0) {
+        mbar_expect_tx(bar_meta, d.meta_words * 4u);
+        bulk_g2s(smem_u32(smem + TS_SMEM_META), p.meta + d.meta_off, d.meta_words * 4u, bar_meta);
     }
 
-    // ---------------------------------- consumers ------------------------------------------------------
     const int c0 = b * p.cols_per_block;
     const int ncols = min(p.cols_per_block, p.N - c0);
     const int t0 = j * p.tiles_per_cta;
     const int ntiles = min(p.tiles_per_cta, p.tiles - t0);
-    const int nlists = 2 * ncols;
+    const int nsubs = (ncols + p.sub_cols - 1) / p.sub_cols;
     const int lpl = 1 << p.lpl_log2;
-    const int lists_per_unit = 32 >> p.lpl_log2;
-    const int nunits = (nlists + lists_per_unit - 1) / lists_per_unit;
-    const uint32_t ring_mask = (uint32_t)p.nstages * TS_STAGE_VECS - 1u;   // nstages is a power of two
+    const bool direct = p.k_splits == 1 && p.tiles_per_cta == 1;   // the block's sums are final: no scratch at all
+
+    // sub-blocks whose sums fit in the accumulator area at once (the area holds 16 * TS_MAX_SUB_COLS cells)
+    const int subs_per_wave = max(1, (16 * TS_MAX_SUB_COLS) / (MP * p.sub_cols));
+    for (int i = tid; i < 16 * TS_MAX_SUB_COLS; i += NT) acc_s[i] = 0;
 
     Gatherer<ACC, MP> gat;
-    gat.init(lane);
-
-    // everything below reads X or writes scratch / Y: order it behind the previous kernel in the stream
-    pdl_wait();
+    gat.init(table, lane);
 
     bool alive = bounded_wait(bar_meta, 0, flags);
     alive = __all_sync(0xffffffffu, alive);
     if (!alive && lane == 0) atomicExch(p.status, TS_ERR_META_WAIT);
+    TS_STAMP(2);
+
+    // Weights do not depend on the previous kernel.  Pull the block's whole index range towards L2 now (a
+    // bounded amount: long ranges are picked up by the loads themselves), and start this warp's first index
+    // loads, before waiting for that kernel.
+    if (tid == 0) {
+        const char* g = (const char*)(p.stream + d.stream_off);
+        const size_t bytes = min((size_t)d.nvec * 16u, (size_t)TS_L2_PREFETCH_BYTES);
+        for (size_t o = 0; o < bytes; o += 16384) l2_prefetch(g + o, (uint32_t)min((size_t)16384, bytes - o));
+    }
+    const uint4* gstream = p.stream + d.stream_off;
+    uint4 buf[D], buf2[D];
+    bool pre = false;
+    if (alive) {
+        // first section of the block, group `warp`
+        const uint32_t* sec = meta;
+        const uint32_t ndiag = sec[1], nl = sec[2];
+        const uint32_t* diag = sec + TS_SEC_HEADER;
+        const uint32_t pos = (uint32_t)warp * 32u + lane;
+        if ((uint32_t)warp * 32u < (nl << p.lpl_log2)) {
+            const uint32_t li = pos >> p.lpl_log2;
+            const int len = li < nl ? (int)(diag[ndiag + 1 + li] >> 16) : 0;
+            const uint4* ptr = gstream + sec[0] + pos;
+#pragma unroll
+            for (int dd = 0; dd < D; ++dd)
+                if (dd < len) buf[dd] = __ldcs(ptr + diag[dd]);
+            pre = true;
+        }
+    }
+    TS_STAMP(7);
+
+    // everything below reads X or writes scratch / Y: order it behind the previous kernel in the stream
+    pdl_wait();
+    TS_STAMP(1);
 
     ACC* partial = (ACC*)p.partial;
+    uint32_t x_phase = 0;
+    const uint32_t* sec = meta;   // walks the block's section tables in processing order
 
     for (int ti = 0; ti < ntiles; ++ti) {
-        if (ti > 0) named_bar(1, CT);   // all gathers of the previous tile are done
+        if (ti > 0) __syncthreads();   // all gathers of the previous tile are done
         // ---- fill the activation table for rows [kbase, kbase+T) plus the zero row T ----
         {
             const int kbase = (t0 + ti) * p.T;
+            const int rows_here = min(p.T, p.K - kbase);
             const int slots = (p.T + 1) * 8;
-            for (int s = tid; s < slots; s += CT) {
-                const int k = s >> 3, q = s & 7;
-                const int kg = kbase + k;
-                const bool live = (k < p.T) && (kg < p.K);
-                struct alignas(16) P4 {
-                    ACC a, b, c, d;
-                } v;
-                v.a = v.b = v.c = v.d = 0;
-                if (live) {
-                    if (EB == 4) {
-                        v.a = load_act<ACC>(p.X, p.x_dtype, p.x_layout ? (size_t)kg * p.x_ld : (size_t)kg);
-                        v.b = v.c = v.d = v.a;
-                    } else if (EB == 8) {
-                        v.a = load_act<ACC>(p.X, p.x_dtype, p.x_layout ? (size_t)kg * p.x_ld : (size_t)kg);
-                        if (p.M > 1) v.b = load_act<ACC>(p.X, p.x_dtype, p.x_layout ? (size_t)kg * p.x_ld + 1 : (size_t)p.x_ld + kg);
-                        v.c = v.a;
-                        v.d = v.b;
-                    } else {
-                        const int m0 = 4 * (q % NCH);
-                        ACC t[4];
+            if (p.x_tma) {
+                // raw rows come in by bulk async copies (TMA) and are expanded from shared memory
+                const uint32_t e = act_bytes(p.x_dtype);
+                const int kc = min(p.T, (int)((TS_STAGE_BYTES / (p.M * e)) / 64u * 64u));
+                for (int k0 = 0; k0 < rows_here; k0 += kc) {
+                    const int n = min(kc, rows_here - k0);
+                    if (tid == 0) {
+                        mbar_expect_tx(bar_x, (uint32_t)p.M * n * e);
+                        for (int m = 0; m < p.M; ++m)
+                            bulk_g2s(smem_u32(stage) + (uint32_t)m * kc * e, (const char*)p.X + ((size_t)m * p.x_ld + kbase + k0) * e, n * e, bar_x);
+                    }
+                    if (alive) {
+                        alive = __all_sync(0xffffffffu, bounded_wait(bar_x, x_phase, flags));
+                        if (!alive && lane == 0) atomicExch(p.status, TS_ERR_X_WAIT);
+                    }
+                    x_phase ^= 1u;
+                    // one table row (128 bytes) per lane: its 8 chunks are written in an order rotated by the
+                    // lane number, so that the 8 lanes of a quarter-warp always write 8 different bank groups
+                    for (int k = k0 + tid; k < k0 + n; k += NT) {
+                        ACC val[MP];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int m = m0 + i;
-                            t[i] = m < p.M ? load_act<ACC>(p.X, p.x_dtype, p.x_layout ? (size_t)kg * p.x_ld + m : (size_t)m * p.x_ld + kg) : (ACC)0;
+                        for (int m = 0; m < MP; ++m) val[m] = m < p.M ? staged_act<ACC>(stage, p.x_dtype, (uint32_t)(m * kc + (k - k0))) : (ACC)0;
+                        fill_row<ACC, MP>(table, k, lane, val);
+                    }
+                    if (k0 + kc < rows_here) __syncthreads();   // the staging buffer is reused by the next chunk
+                }
+                for (int k = rows_here + tid; k <= p.T; k += NT) {
+                    ACC val[MP];
+#pragma unroll
+                    for (int m = 0; m < MP; ++m) val[m] = 0;
+                    fill_row<ACC, MP>(table, k, lane, val);
+                }
+            } else {
+                // generic path (column-major or unaligned activations): loads straight from global memory
+                for (int k = tid; k <= p.T; k += NT) {
+                    const int kg = kbase + k;
+                    const bool live = k < p.T && kg < p.K;
+                    ACC val[MP];
+#pragma unroll
+                    for (int m = 0; m < MP; ++m)
+                        val[m] = (live && m < p.M) ? load_act_cg<ACC>(p.X, p.x_dtype, p.x_layout ? (size_t)kg * p.x_ld + m : (size_t)m * p.x_ld + kg)
+                                                   : (ACC)0;
+                    fill_row<ACC, MP>(table, k, lane, val);
+                }
+            }
+        }
+        __syncthreads();
+        if (ti == 0) TS_STAMP(3);
+
+        // ---- the tile's sections, in waves of as many sub-blocks as have room for their sums in shared memory;
+        // inside a wave every warp takes the next group of 32 lanes from a shared counter, so no warp idles
+        // while another works through a second group ----
+        for (int sub0 = 0; sub0 < nsubs; sub0 += subs_per_wave) {
+            const int nsw = min(subs_per_wave, nsubs - sub0);
+            const uint32_t* wave_sec = sec;
+            // groups in this wave, and the first section after it
+            uint32_t wave_groups = 0;
+            {
+                const uint32_t* q = sec;
+                for (int k = 0; k < nsw; ++k) {
+                    wave_groups += ((q[2] << p.lpl_log2) + 31u) >> 5;
+                    q += TS_SEC_HEADER + q[1] + 1 + q[2];
+                }
+                sec = q;
+            }
+            uint32_t f = (uint32_t)warp;   // first group: static, so that it could be prefetched; then the counter
+            while (f < wave_groups && alive) {
+                // locate section and group of flat index f
+                const uint32_t* sc = wave_sec;
+                uint32_t g = f;
+                int slot = 0;
+                for (;; ++slot) {
+                    const uint32_t ng = ((sc[2] << p.lpl_log2) + 31u) >> 5;
+                    if (g < ng) break;
+                    g -= ng;
+                    sc += TS_SEC_HEADER + sc[1] + 1 + sc[2];
+                }
+                const uint32_t ndiag = sc[1], nl = sc[2];
+                const uint32_t* diag = sc + TS_SEC_HEADER;
+                const uint32_t* lists = diag + ndiag + 1;
+                const uint32_t pos = g * 32u + lane;             // lane position in the section's sorted order
+                const uint32_t li = pos >> p.lpl_log2;           // sorted list this lane works for
+                const uint32_t word = li < nl ? lists[li] : 0u;
+                const int len = (int)(word >> 16);               // vectors this lane owns
+                const int steps = __shfl_sync(0xffffffffu, len, 0);   // lane 0 has the longest list of the group
+                const uint4* ptr = gstream + sc[0] + pos;
+                ACC acc[MP];
+#pragma unroll
+                for (int i = 0; i < MP; ++i) acc[i] = 0;
+                // Two register batches of D vectors each.  All loads of a batch are issued back to back, before
+                // the other batch is consumed, so D loads per lane are in flight while the gathers of the other
+                // D run.  (A load issued conditionally inside the loop that consumes its neighbours does not
+                // overlap with them: measured at about half the bandwidth.)
+                auto load_batch = [&](uint4 (&bf)[D], int base) {
+#pragma unroll
+                    for (int dd = 0; dd < D; ++dd)
+                        if (base + dd < len) bf[dd] = __ldcs(ptr + diag[base + dd]);
+                };
+                auto use_batch = [&](const uint4 (&bf)[D], int base) {
+#pragma unroll
+                    for (int dd = 0; dd < D; ++dd)
+                        if (base + dd < len) gat.add8(bf[dd], acc);
+                };
+                if (!pre) load_batch(buf, 0);
+                pre = false;
+                for (int i0 = 0; i0 < steps; i0 += 2 * D) {
+                    load_batch(buf2, i0 + D);
+                    use_batch(buf, i0);
+                    load_batch(buf, i0 + 2 * D);
+                    use_batch(buf2, i0 + D);
+                }
+                gat.unrotate(acc);
+                for (int o = 1; o < lpl; o <<= 1) {   // lanes that share a list
+#pragma unroll
+                    for (int i = 0; i < MP; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+                }
+                if ((lane & (lpl - 1)) == 0 && li < nl) {
+                    // a column's + list and - list are the only two contributions to its cell between two
+                    // flushes, so the order in which they arrive cannot change the sum
+                    ACC* cell = acc_s + slot * (MP * p.sub_cols) + (word & 0x7fffu);
+                    const bool neg = (word & 0x8000u) != 0;
+#pragma unroll
+                    for (int m = 0; m < MP; ++m)
+                        if (m < p.M) atomicAdd(cell + m * p.sub_cols, neg ? -acc[m] : acc[m]);
+                }
+                // next group
+                uint32_t nf = 0;
+                if (lane == 0) nf = (uint32_t)atomicAdd((int*)&flags[2], 1);
+                f = __shfl_sync(0xffffffffu, nf, 0);
+            }
+            __syncthreads();
+            // ---- flush the wave's sums ----
+            for (int k = 0; k < nsw; ++k) {
+                const int sub = sub0 + k;
+                const int ns = min(p.sub_cols, ncols - sub * p.sub_cols);
+                const int gcol0 = c0 + sub * p.sub_cols;
+                ACC* as = acc_s + k * (MP * p.sub_cols);
+                if (direct) {
+                    if (p.epilogue == 0) {
+                        for (int i = tid; i < p.M * ns; i += NT) {
+                            const int m = i / ns, c = i - m * ns;
+                            const ACC sv = as[m * p.sub_cols + c];
+                            as[m * p.sub_cols + c] = 0;
+                            if (p.y_dtype == TLLM_I32) ((int*)p.Y)[(size_t)m * p.y_ld + gcol0 + c] = (int)sv;
+                            else store_out(p.Y, p.y_dtype, (size_t)m * p.y_ld + gcol0 + c, (float)sv * p.scale);
                         }
-                        v.a = t[0];
-                        v.b = t[1];
-                        v.c = t[2];
-                        v.d = t[3];
+                    } else {
+                        const int np = ns >> 1;
+                        for (int i = tid; i < p.M * np; i += NT) {
+                            const int m = i / np, c = i - m * np;
+                            const float g = (float)as[m * p.sub_cols + 2 * c], up = (float)as[m * p.sub_cols + 2 * c + 1];
+                            as[m * p.sub_cols + 2 * c] = 0;
+                            as[m * p.sub_cols + 2 * c + 1] = 0;
+                            store_out(p.Y, p.y_dtype, (size_t)m * p.y_ld + (gcol0 >> 1) + c, silu_mul(g * p.scale, up * p.scale2));
+                        }
                     }
-                }
-                *(P4*)(table + (size_t)s * 16) = v;
-            }
-        }
-        named_bar(1, CT);
-
-        const uint32_t* vs = meta + (size_t)ti * (nlists + 1);
-        for (int u = warp; u < nunits && alive; u += NW) {
-            const int l0 = u * lists_per_unit;
-            const int l1 = min(nlists, l0 + lists_per_unit);
-            const uint32_t ubeg = vs[l0], uend = vs[l1];
-            if (uend > ubeg) {
-                for (uint32_t c = ubeg / TS_STAGE_VECS; c <= (uend - 1) / TS_STAGE_VECS && alive; ++c)
-                    alive = bounded_wait(bar_full + 8 * (c % (uint32_t)p.nstages), (c / (uint32_t)p.nstages) & 1, flags);
-                alive = __all_sync(0xffffffffu, alive);
-                if (!alive) {
-                    if (lane == 0) atomicExch(p.status, TS_ERR_FULL_WAIT);
-                    break;
-                }
-            }
-            ACC acc[MP];
-#pragma unroll
-            for (int i = 0; i < MP; ++i) acc[i] = 0;
-            const int mylist = l0 + (lane >> p.lpl_log2);
-            if (mylist < l1) {
-                const uint32_t vend = vs[mylist + 1];
-                for (uint32_t v = vs[mylist] + (uint32_t)(lane & (lpl - 1)); v < vend; v += (uint32_t)lpl) {
-                    const uint4 qv = ring[v & ring_mask];
-                    gat.add(table, qv.x & 0xffffu, acc);
-                    gat.add(table, qv.x >> 16, acc);
-                    gat.add(table, qv.y & 0xffffu, acc);
-                    gat.add(table, qv.y >> 16, acc);
-                    gat.add(table, qv.z & 0xffffu, acc);
-                    gat.add(table, qv.z >> 16, acc);
-                    gat.add(table, qv.w & 0xffffu, acc);
-                    gat.add(table, qv.w >> 16, acc);
-                }
-            }
-            gat.unrotate(acc);
-            if (mylist & 1) {
-#pragma unroll
-                for (int i = 0; i < MP; ++i) acc[i] = -acc[i];
-            }
-            // sum over the 2*lpl lanes of a column: its + list lanes and its - list lanes
-            for (int o = 1; o < 2 * lpl; o <<= 1) {
-#pragma unroll
-                for (int i = 0; i < MP; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
-            }
-            if ((lane & (2 * lpl - 1)) == 0 && mylist < l1) {
-                const int col = c0 + (mylist >> 1);
-#pragma unroll
-                for (int m = 0; m < MP; ++m) {
-                    if (m < p.M) {
-                        ACC* dst = partial + ((size_t)j * p.M + m) * p.N + col;
-                        *dst = ti > 0 ? *dst + acc[m] : acc[m];
+                } else {
+                    for (int i = tid; i < p.M * ns; i += NT) {
+                        const int m = i / ns, c = i - m * ns;
+                        const ACC sv = as[m * p.sub_cols + c];
+                        as[m * p.sub_cols + c] = 0;
+                        // the same thread owns this cell of the block's scratch slice in every tile
+                        ACC* dst = partial + ((size_t)j * p.M + m) * p.N + gcol0 + c;
+                        *dst = ti > 0 ? *dst + sv : sv;
                     }
                 }
             }
-            // hand the consumed vectors back to the producer, stage by stage
-            __syncwarp();
-            if (lane == 0 && uend > ubeg) {
-                for (uint32_t c = ubeg / TS_STAGE_VECS; c <= (uend - 1) / TS_STAGE_VECS; ++c) {
-                    const uint32_t lo = max(ubeg, c * TS_STAGE_VECS), hi = min(uend, (c + 1) * TS_STAGE_VECS);
-                    mbar_arrive_n(bar_empty + 8 * (c % (uint32_t)p.nstages), hi - lo);
-                }
-            }
+            if (tid == 0) flags[2] = NW;   // the counter hands out groups NW, NW+1, ... of the next wave
+            __syncthreads();
         }
     }
+    TS_STAMP(4);
 
-    // ---- split-K: the last block of this column block to arrive adds the partial sums in split order ----
-    __threadfence();
-    named_bar(1, CT);
-    if (tid == 0) {
-        const unsigned int prev = atomicAdd(p.counters + b, 1u);
-        flags[1] = (prev == (unsigned int)p.k_splits - 1u) ? 1 : 0;
-    }
-    named_bar(1, CT);
-    if (flags[1]) {
-        __threadfence();
-        if (p.epilogue == 0) {
-            for (int i = tid; i < p.M * ncols; i += CT) {
-                const int m = i / ncols, c = i - m * ncols;
+    if (!direct) {
+        bool finish = true;
+        if (p.k_splits > 1) {
+            // split-K: the last block of this column block to arrive adds the partial sums in split order
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                const unsigned int prev = atomicAdd(p.counters + b, 1u);
+                flags[1] = (prev == (unsigned int)p.k_splits - 1u) ? 1 : 0;
+            }
+            __syncthreads();
+            finish = flags[1] != 0;
+            if (finish) __threadfence();
+        }
+        TS_STAMP(5);
+        if (finish) {
+            const int first = p.k_splits > 1 ? 0 : j, count = p.k_splits > 1 ? p.k_splits : 1;
+            auto total = [&](int m, int c) -> ACC {
                 ACC s = 0;
-                for (int js = 0; js < p.k_splits; ++js) s += __ldcg(partial + ((size_t)js * p.M + m) * p.N + c0 + c);
-                if (p.y_dtype == TLLM_I32) ((int*)p.Y)[(size_t)m * p.y_ld + c0 + c] = (int)s;
-                else store_out(p.Y, p.y_dtype, (size_t)m * p.y_ld + c0 + c, (float)s * p.scale);
-            }
-        } else {
-            const int npairs = ncols >> 1;
-            for (int i = tid; i < p.M * npairs; i += CT) {
-                const int m = i / npairs, c = i - m * npairs;
-                float g = 0.f, up = 0.f;
-                for (int js = 0; js < p.k_splits; ++js) {
-                    const ACC* row = partial + ((size_t)js * p.M + m) * p.N + c0 + 2 * c;
-                    g += (float)__ldcg(row);
-                    up += (float)__ldcg(row + 1);
+                for (int js = 0; js < count; ++js) s += __ldcg(partial + ((size_t)(first + js) * p.M + m) * p.N + c0 + c);
+                return s;
+            };
+            if (p.epilogue == 0) {
+                for (int i = tid; i < p.M * ncols; i += NT) {
+                    const int m = i / ncols, c = i - m * ncols;
+                    const ACC s = total(m, c);
+                    if (p.y_dtype == TLLM_I32) ((int*)p.Y)[(size_t)m * p.y_ld + c0 + c] = (int)s;
+                    else store_out(p.Y, p.y_dtype, (size_t)m * p.y_ld + c0 + c, (float)s * p.scale);
                 }
-                store_out(p.Y, p.y_dtype, (size_t)m * p.y_ld + (c0 >> 1) + c, silu_mul(g * p.scale, up * p.scale2));
+            } else {
+                const int npairs = ncols >> 1;
+                for (int i = tid; i < p.M * npairs; i += NT) {
+                    const int m = i / npairs, c = i - m * npairs;
+                    const float g = (float)total(m, 2 * c), up = (float)total(m, 2 * c + 1);
+                    store_out(p.Y, p.y_dtype, (size_t)m * p.y_ld + (c0 >> 1) + c, silu_mul(g * p.scale, up * p.scale2));
+                }
             }
+            if (p.k_splits > 1 && tid == 0) p.counters[b] = 0u;
         }
-        if (tid == 0) p.counters[b] = 0u;
     }
+    TS_STAMP(6);
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -379,22 +379,31 @@ const char* decode_cpu_format(int kind, int group, int chunk, const int32_t* met
 // ------------------------------------------------------------------------------------------------------
 namespace {
 
-int pow2_floor(int v) {
-    int p = 1;
-    while (p * 2 <= v) p *= 2;
-    return p;
-}
 int pow2_ceil(int v) {
     int p = 1;
     while (p < v) p *= 2;
     return p;
 }
 
+struct ListRef {
+    int col;        // column within the sub-block
+    int sign;       // 0: +1 list, 1: -1 list
+    const int32_t* first;
+    int n;          // ids
+    int nvec() const { return (n + TS_IDS_PER_VEC - 1) / TS_IDS_PER_VEC; }
+};
+
+// upper bound of the table words of one block (a list has at most tile_rows/8 + 1 vectors)
+size_t meta_words_of(int ncols, int sub_cols, int T, int ntiles) {
+    size_t words = 0;
+    for (int c = 0; c < ncols; c += sub_cols) words += TS_SEC_HEADER + (size_t)(T / TS_IDS_PER_VEC + 2) + 2 * (size_t)std::min(sub_cols, ncols - c);
+    return words * (size_t)ntiles;
+}
+
 }  // namespace
 
 const char* ts_pack_dense(const int8_t* w, int inners, int columns, const tllm_pack_opts* opts, int num_sms,
                           TsHostImage* out) {
-    static thread_local std::string err;
     if (!w || inners <= 0 || columns <= 0) return "pack: bad matrix shape";
     if ((int64_t)inners * columns > ((int64_t)1 << 40)) return "pack: matrix too large";
     tllm_pack_opts o{};
@@ -404,21 +413,28 @@ const char* ts_pack_dense(const int8_t* w, int inners, int columns, const tllm_p
     if (T > inners) T = (inners + 7) / 8 * 8;
     int ctas = o.num_ctas > 0 ? o.num_ctas : num_sms;
     if (ctas <= 0 || ctas > TS_MAX_CTAS) return "pack: num_ctas out of range";
+    int lpl = o.lanes_per_list > 0 ? o.lanes_per_list : 1;   // 0: chosen below, once the column blocks are known
+    if (lpl < 1 || lpl > 16 || (lpl & (lpl - 1))) return "pack: lanes_per_list must be 1, 2, 4, 8 or 16";
     const int tiles = tiles_of(inners, T);
 
     // ---- schedule: k_splits x col_blocks blocks, each block owns tiles_per_cta tiles of one column block
-    int best_tpc = 1, best_nb = 1;
+    int best_tpc = 0, best_nb = 1;
     double best_cost = 1e300;
     for (int tpc = 1; tpc <= tiles; ++tpc) {
         const int splits = (tiles + tpc - 1) / tpc;
         if (splits > ctas) continue;
-        int nb = std::min(ctas / splits, columns);
-        if (nb < 1) continue;
+        if (o.k_splits > 0 && tpc != (tiles + o.k_splits - 1) / o.k_splits) continue;
+        int nb = std::min(ctas / splits, (columns + 1) / 2);
+        if (nb < 1) nb = 1;
         // column blocks hold an even number of columns, so that (gate, up) column pairs never straddle one
-        auto cols_for = [&](int blocks) { return ((columns + blocks - 1) / blocks + 1) & ~1; };
+        // (and, when wide enough, a multiple of 16 columns = 32 lists, so that no unit is left with idle lanes)
+        auto cols_for = [&](int blocks) {
+            const int c = (columns + blocks - 1) / blocks;
+            return c >= 64 ? (c + 15) & ~15 : (c + 1) & ~1;
+        };
         int bc = cols_for(nb);
-        // keep the per-block list table inside its shared-memory budget
-        while ((size_t)tpc * (2 * (size_t)bc + 1) * 4 + 16 > TS_MAX_META_BYTES) {
+        // keep the per-block unit table inside its shared-memory budget
+        while (meta_words_of(bc, std::min(bc, TS_MAX_SUB_COLS), T, tpc) * 4 + 16 > TS_MAX_META_BYTES && bc > 2) {
             ++nb;
             bc = cols_for(nb);
         }
@@ -436,7 +452,7 @@ const char* ts_pack_dense(const int8_t* w, int inners, int columns, const tllm_p
             best_nb = nb;
         }
     }
-    if (best_cost >= 1e300) return "pack: no schedule fits (matrix too wide for one wave of blocks)";
+    if (best_tpc == 0) return "pack: no schedule fits (matrix too wide for the block budget)";
     TsLayout& L = out->lay;
     L = TsLayout{};
     L.inners = inners;
@@ -445,148 +461,194 @@ const char* ts_pack_dense(const int8_t* w, int inners, int columns, const tllm_p
     L.tiles = tiles;
     L.tiles_per_cta = best_tpc;
     L.k_splits = (tiles + best_tpc - 1) / best_tpc;
-    L.cols_per_block = ((columns + best_nb - 1) / best_nb + 1) & ~1;
+    {
+        const int c = (columns + best_nb - 1) / best_nb;
+        L.cols_per_block = c >= 64 ? (c + 15) & ~15 : (c + 1) & ~1;
+    }
     L.col_blocks = (columns + L.cols_per_block - 1) / L.cols_per_block;
     L.num_ctas = L.col_blocks * L.k_splits;
+    L.sub_cols = std::min(L.cols_per_block, TS_MAX_SUB_COLS);
+    if (o.lanes_per_list <= 0) {
+        // One lane per list keeps padding and shuffles lowest.  Narrow column blocks have too few lists to
+        // fill the lanes of a unit or to give every warp a unit: there several lanes share a list.
+        const int nlists = 2 * L.sub_cols;
+        lpl = std::min(16, std::max(1, pow2_ceil((12 * 32 + nlists - 1) / nlists)));
+    }
+    L.lanes_per_list = lpl;
 
     ColumnLists<int8_t> cl(w, inners, columns);
     L.nnz = (int64_t)cl.pos_row.size() + (int64_t)cl.neg_row.size();
 
-    // ---- lanes per list: a lane should own a handful of vectors, and a (block, tile) should offer at
-    // least one unit per consumer warp
-    int lpl = o.lanes_per_list;
-    if (lpl <= 0) {
-        const double lists = 2.0 * columns * tiles;
-        const double vec_per_list = (double)L.nnz / 8.0 / lists + 0.5;
-        lpl = pow2_floor(std::max(1, (int)(vec_per_list / 4.0)));
-        const int want = pow2_ceil((31 * 16 + L.cols_per_block - 1) / L.cols_per_block);
-        lpl = std::max(lpl, want);
-        lpl = std::min(lpl, 16);
-    }
-    if (lpl < 1 || lpl > 16 || (lpl & (lpl - 1))) return "pack: lanes_per_list must be 1, 2, 4, 8 or 16";
-
-    // ---- emit, block by block; retry with more lanes per list if a unit would not fit in the ring
-    for (;; lpl *= 2) {
-        if (lpl > 16) return "pack: a work unit exceeds the shared-memory ring even at 16 lanes per list";
-        L.lanes_per_list = lpl;
-        out->stream.clear();
-        out->vstart.clear();
-        const int lists_per_unit = 32 / lpl;
-        bool unit_too_big = false;
-        for (int j = 0; j < L.k_splits && !unit_too_big; ++j) {
-            for (int b = 0; b < L.col_blocks && !unit_too_big; ++b) {
-                const int cta = j * L.col_blocks + b;
-                const int c0 = b * L.cols_per_block, c1 = std::min(columns, c0 + L.cols_per_block);
-                const int t0 = j * L.tiles_per_cta, t1 = std::min(tiles, t0 + L.tiles_per_cta);
-                while (out->stream.size() % (8 * TS_IDS_PER_VEC)) out->stream.push_back((uint16_t)T);   // 128-byte start
-                while (out->vstart.size() % 4) out->vstart.push_back(0);
-                TsCtaDesc& d = L.cta[cta];
-                d.stream_off = (uint32_t)(out->stream.size() / TS_IDS_PER_VEC);
-                d.meta_off = (uint32_t)out->vstart.size();
-                const size_t base = out->stream.size();
-                for (int t = t0; t < t1; ++t) {
-                    const int lo = t * T, hi = lo + T;
-                    const size_t tile_meta = out->vstart.size();
-                    for (int c = c0; c < c1; ++c) {
-                        for (int s = 0; s < 2; ++s) {
-                            const std::vector<int64_t>& ptr = s ? cl.neg_ptr : cl.pos_ptr;
-                            const std::vector<int32_t>& rows = s ? cl.neg_row : cl.pos_row;
-                            out->vstart.push_back((uint32_t)((out->stream.size() - base) / TS_IDS_PER_VEC));
+    out->stream.clear();
+    out->meta.clear();
+    std::vector<ListRef> lists;
+    auto pad_vectors_to = [&](size_t mult) {
+        while ((out->stream.size() / TS_IDS_PER_VEC) % mult) out->stream.insert(out->stream.end(), TS_IDS_PER_VEC, (uint16_t)T);
+    };
+    for (int j = 0; j < L.k_splits; ++j) {
+        for (int b = 0; b < L.col_blocks; ++b) {
+            const int cta = j * L.col_blocks + b;
+            const int c0 = b * L.cols_per_block, c1 = std::min(columns, c0 + L.cols_per_block);
+            const int t0 = j * L.tiles_per_cta, t1 = std::min(tiles, t0 + L.tiles_per_cta);
+            while (out->meta.size() % 4) out->meta.push_back(0);
+            pad_vectors_to(32);
+            TsCtaDesc& d = L.cta[cta];
+            d.stream_off = (uint32_t)(out->stream.size() / TS_IDS_PER_VEC);
+            d.meta_off = (uint32_t)out->meta.size();
+            const size_t base = out->stream.size();
+            for (int t = t0; t < t1; ++t) {
+                const int lo = t * T, hi = lo + T;
+                for (int s0 = c0; s0 < c1; s0 += L.sub_cols) {
+                    const int s1 = std::min(c1, s0 + L.sub_cols);
+                    lists.clear();
+                    for (int c = s0; c < s1; ++c)
+                        for (int sg = 0; sg < 2; ++sg) {
+                            const std::vector<int64_t>& ptr = sg ? cl.neg_ptr : cl.pos_ptr;
+                            const std::vector<int32_t>& rows = sg ? cl.neg_row : cl.pos_row;
                             const int32_t* first = std::lower_bound(rows.data() + ptr[c], rows.data() + ptr[c + 1], lo);
                             const int32_t* last = std::lower_bound(first, rows.data() + ptr[c + 1], hi);
-                            for (const int32_t* p = first; p < last; ++p) out->stream.push_back((uint16_t)(*p - lo));
-                            while (out->stream.size() % TS_IDS_PER_VEC) out->stream.push_back((uint16_t)T);
+                            lists.push_back(ListRef{c - s0, sg, first, (int)(last - first)});
                         }
+                    // longest first; ties keep column order, so the layout is a pure function of W
+                    auto steps_of = [&](const ListRef& l) { return (l.nvec() + lpl - 1) / lpl; };
+                    std::stable_sort(lists.begin(), lists.end(), [&](const ListRef& a, const ListRef& b2) { return steps_of(a) > steps_of(b2); });
+                    const int nl = (int)lists.size();
+                    const int ndiag = nl ? steps_of(lists[0]) : 0;
+                    pad_vectors_to(32);
+                    const size_t sec_base = out->stream.size();
+                    out->meta.push_back((uint32_t)((sec_base - base) / TS_IDS_PER_VEC));
+                    out->meta.push_back((uint32_t)ndiag);
+                    out->meta.push_back((uint32_t)nl);
+                    out->meta.push_back(0);
+                    const size_t diag_words = out->meta.size();
+                    out->meta.resize(diag_words + ndiag + 1);
+                    int live = nl;   // lists that still have a vector in this diagonal: a prefix of the sorted order
+                    for (int i = 0; i < ndiag; ++i) {
+                        while (live > 0 && steps_of(lists[live - 1]) <= i) --live;
+                        pad_vectors_to(8);
+                        out->meta[diag_words + i] = (uint32_t)((out->stream.size() - sec_base) / TS_IDS_PER_VEC);
+                        for (int l = 0; l < live; ++l)
+                            for (int jj = 0; jj < lpl; ++jj) {
+                                const int v = i * lpl + jj;
+                                for (int e = 0; e < TS_IDS_PER_VEC; ++e) {
+                                    const int at = v * TS_IDS_PER_VEC + e;
+                                    out->stream.push_back(at < lists[l].n ? (uint16_t)(lists[l].first[at] - lo) : (uint16_t)T);
+                                }
+                            }
                     }
-                    out->vstart.push_back((uint32_t)((out->stream.size() - base) / TS_IDS_PER_VEC));
-                    // unit size check
-                    const int nlists = 2 * (c1 - c0);
-                    for (int l0 = 0; l0 < nlists; l0 += lists_per_unit) {
-                        const int l1 = std::min(nlists, l0 + lists_per_unit);
-                        if (out->vstart[tile_meta + l1] - out->vstart[tile_meta + l0] > (uint32_t)(TS_RING_VECS - TS_STAGE_VECS))
-                            unit_too_big = true;
-                    }
+                    pad_vectors_to(8);
+                    out->meta[diag_words + ndiag] = (uint32_t)((out->stream.size() - sec_base) / TS_IDS_PER_VEC);
+                    for (const ListRef& l : lists)
+                        out->meta.push_back((uint32_t)(l.col | (l.sign << 15)) | ((uint32_t)steps_of(l) << 16));
                 }
-                d.nvec = (uint32_t)((out->stream.size() - base) / TS_IDS_PER_VEC);
-                while (out->vstart.size() % 4) out->vstart.push_back(0);
-                d.meta_words = (uint32_t)(out->vstart.size() - d.meta_off);
-                if ((size_t)d.meta_words * 4 > TS_MAX_META_BYTES) return "pack: list table exceeds its shared-memory budget";
             }
+            pad_vectors_to(32);
+            d.nvec = (uint32_t)((out->stream.size() - base) / TS_IDS_PER_VEC);
+            while (out->meta.size() % 4) out->meta.push_back(0);
+            d.meta_words = (uint32_t)(out->meta.size() - d.meta_off);
+            if ((size_t)d.meta_words * 4 > TS_MAX_META_BYTES) return "pack: section table exceeds its shared-memory budget";
         }
-        if (!unit_too_big) break;
-        if (o.lanes_per_list > 0) return "pack: lanes_per_list too small for this density (a work unit exceeds the ring)";
     }
-    // the bulk copy of a block's last stage may be shorter than a stage but never reads past the array
     L.total_vecs = (int64_t)(out->stream.size() / TS_IDS_PER_VEC);
     if (L.total_vecs >= ((int64_t)1 << 32)) return "pack: stream exceeds 64 GiB";
-    (void)err;
     return nullptr;
 }
 
-void ts_unpack_dense(const TsHostImage& img, int8_t* w) {
+namespace {
+
+// Walks every section of an image: f(block descriptor, tile, first column of the sub-block, columns in it, section words)
+template <typename F>
+void for_each_section(const TsHostImage& img, F&& f) {
     const TsLayout& L = img.lay;
-    std::memset(w, 0, (size_t)L.inners * L.columns);
     for (int j = 0; j < L.k_splits; ++j)
         for (int b = 0; b < L.col_blocks; ++b) {
             const TsCtaDesc& d = L.cta[j * L.col_blocks + b];
             const int c0 = b * L.cols_per_block, c1 = std::min(L.columns, c0 + L.cols_per_block);
             const int t0 = j * L.tiles_per_cta, t1 = std::min(L.tiles, t0 + L.tiles_per_cta);
-            const uint32_t* vs = img.vstart.data() + d.meta_off;
-            for (int t = t0; t < t1; ++t, vs += 2 * (c1 - c0) + 1)
-                for (int c = c0; c < c1; ++c)
-                    for (int s = 0; s < 2; ++s) {
-                        const int l = 2 * (c - c0) + s;
-                        for (uint32_t v = vs[l]; v < vs[l + 1]; ++v)
-                            for (int e = 0; e < TS_IDS_PER_VEC; ++e) {
-                                const int id = img.stream[((size_t)d.stream_off + v) * TS_IDS_PER_VEC + e];
-                                if (id < L.tile_rows && t * L.tile_rows + id < L.inners)
-                                    w[(size_t)(t * L.tile_rows + id) * L.columns + c] += s ? -1 : 1;
-                            }
-                    }
+            const uint32_t* sec = img.meta.data() + d.meta_off;
+            for (int t = t0; t < t1; ++t)
+                for (int s0 = c0; s0 < c1; s0 += L.sub_cols) {
+                    const int ns = std::min(L.sub_cols, c1 - s0);
+                    f(d, t, s0, ns, sec);
+                    sec += TS_SEC_HEADER + sec[1] + 1 + sec[2];
+                }
         }
+}
+
+}  // namespace
+
+void ts_unpack_dense(const TsHostImage& img, int8_t* w) {
+    const TsLayout& L = img.lay;
+    std::memset(w, 0, (size_t)L.inners * L.columns);
+    const int lpl = L.lanes_per_list;
+    for_each_section(img, [&](const TsCtaDesc& d, int t, int s0, int, const uint32_t* sec) {
+        const uint32_t ndiag = sec[1], nl = sec[2];
+        const uint32_t* diag = sec + TS_SEC_HEADER;
+        const uint32_t* lists = diag + ndiag + 1;
+        for (uint32_t l = 0; l < nl; ++l) {
+            const uint32_t tag = lists[l] & 0xffffu, steps = lists[l] >> 16;
+            for (uint32_t i = 0; i < steps; ++i)
+                for (int jj = 0; jj < lpl; ++jj) {
+                    const size_t vec = (size_t)d.stream_off + sec[0] + diag[i] + (size_t)l * lpl + jj;
+                    for (int e = 0; e < TS_IDS_PER_VEC; ++e) {
+                        const int id = img.stream[vec * TS_IDS_PER_VEC + e];
+                        if (id < L.tile_rows && t * L.tile_rows + id < L.inners)
+                            w[(size_t)(t * L.tile_rows + id) * L.columns + s0 + (tag & 0x7fff)] += (tag >> 15) ? -1 : 1;
+                    }
+                }
+        }
+    });
 }
 
 const char* ts_validate(const TsHostImage& img) {
     const TsLayout& L = img.lay;
     if (L.num_ctas != L.col_blocks * L.k_splits || L.num_ctas > TS_MAX_CTAS) return "validate: block count";
-    if (L.cols_per_block & 1) return "validate: odd column block";
-    const int lists_per_unit = 32 / L.lanes_per_list;
-    for (int j = 0; j < L.k_splits; ++j)
-        for (int b = 0; b < L.col_blocks; ++b) {
-            const TsCtaDesc& d = L.cta[j * L.col_blocks + b];
-            if (d.stream_off % 8 || d.meta_off % 4 || d.meta_words % 4) return "validate: alignment";
-            if ((size_t)(d.stream_off + d.nvec) * TS_IDS_PER_VEC > img.stream.size()) return "validate: stream range";
-            if ((size_t)d.meta_off + d.meta_words > img.vstart.size()) return "validate: meta range";
-            const int c0 = b * L.cols_per_block, c1 = std::min(L.columns, c0 + L.cols_per_block);
-            const int t0 = j * L.tiles_per_cta, t1 = std::min(L.tiles, t0 + L.tiles_per_cta);
-            if (c1 <= c0 || t1 <= t0) return "validate: empty block";
-            const int nlists = 2 * (c1 - c0);
-            if ((size_t)(t1 - t0) * (nlists + 1) > d.meta_words) return "validate: meta size";
-            const uint32_t* vs = img.vstart.data() + d.meta_off;
-            std::vector<uint32_t> released((d.nvec + TS_STAGE_VECS - 1) / TS_STAGE_VECS + 1, 0);
-            uint32_t expect = 0;
-            for (int t = t0; t < t1; ++t, vs += nlists + 1) {
-                if (vs[0] != expect) return "validate: tiles of a block are not contiguous";
-                for (int l = 0; l < nlists; ++l)
-                    if (vs[l + 1] < vs[l]) return "validate: list offsets not monotone";
-                for (int l0 = 0; l0 < nlists; l0 += lists_per_unit) {
-                    const int l1 = std::min(nlists, l0 + lists_per_unit);
-                    const uint32_t ub = vs[l0], ue = vs[l1];
-                    if (ue - ub > (uint32_t)(TS_RING_VECS - TS_STAGE_VECS)) return "validate: unit exceeds ring";
-                    if (ue > ub)
-                        for (uint32_t c = ub / TS_STAGE_VECS; c <= (ue - 1) / TS_STAGE_VECS; ++c)
-                            released[c] += std::min(ue, (c + 1) * TS_STAGE_VECS) - std::max(ub, c * TS_STAGE_VECS);
-                }
-                expect = vs[nlists];
-            }
-            if (expect != d.nvec) return "validate: lists do not cover the block's range";
-            for (uint32_t c = 0; c * TS_STAGE_VECS < d.nvec; ++c) {
-                const uint32_t want = std::min<uint32_t>(TS_STAGE_VECS, d.nvec - c * TS_STAGE_VECS);
-                if (released[c] != want) return "validate: a ring stage is not handed back exactly once";
-            }
-            for (size_t i = (size_t)d.stream_off * 8; i < (size_t)(d.stream_off + d.nvec) * 8; ++i)
-                if (img.stream[i] > (uint16_t)L.tile_rows) return "validate: row id beyond the zero row";
+    if ((L.cols_per_block & 1) || L.sub_cols > TS_MAX_SUB_COLS || L.sub_cols <= 0) return "validate: column block / sub-block size";
+    if (L.sub_cols < L.cols_per_block && (L.sub_cols & 1)) return "validate: odd sub-block";
+    const int lpl = L.lanes_per_list;
+    if (lpl < 1 || lpl > 16 || (lpl & (lpl - 1))) return "validate: lanes per list";
+    for (int i = 0; i < L.num_ctas; ++i) {
+        const TsCtaDesc& d = L.cta[i];
+        if (d.stream_off % 32 || d.nvec % 32 || d.meta_off % 4 || d.meta_words % 4) return "validate: alignment";
+        if ((size_t)(d.stream_off + d.nvec) * TS_IDS_PER_VEC > img.stream.size()) return "validate: stream range";
+        if ((size_t)d.meta_off + d.meta_words > img.meta.size()) return "validate: table range";
+        if ((size_t)d.meta_words * 4 > TS_MAX_META_BYTES) return "validate: table size";
+    }
+    const char* err = nullptr;
+    std::vector<int> seen;
+    for_each_section(img, [&](const TsCtaDesc& d, int, int, int ns, const uint32_t* sec) {
+        if (err) return;
+        const uint32_t ndiag = sec[1], nl = sec[2];
+        if ((size_t)(sec - (img.meta.data() + d.meta_off)) + TS_SEC_HEADER + ndiag + 1 + nl > d.meta_words) { err = "validate: section table overruns the block's table"; return; }
+        if (nl != (uint32_t)(2 * ns)) { err = "validate: list count"; return; }
+        if (sec[0] % 32) err = "validate: section alignment";
+        const uint32_t* diag = sec + TS_SEC_HEADER;
+        const uint32_t* lists = diag + ndiag + 1;
+        if (sec[0] + diag[ndiag] > d.nvec) err = "validate: section data out of the block's range";
+        seen.assign((size_t)2 * ns, 0);
+        uint32_t prev_steps = 0xffffffffu;
+        for (uint32_t l = 0; l < nl; ++l) {
+            const uint32_t tag = lists[l] & 0xffffu, steps = lists[l] >> 16;
+            if (steps > prev_steps) err = "validate: lists not sorted by length";
+            prev_steps = steps;
+            if (steps > ndiag) err = "validate: list longer than the diagonal count";
+            if ((int)(tag & 0x7fff) >= ns) { err = "validate: column tag out of range"; return; }
+            seen[(size_t)2 * (tag & 0x7fff) + (tag >> 15)]++;
         }
+        for (int v : seen)
+            if (v != 1) err = "validate: a list is missing or duplicated";
+        // every diagonal holds exactly the lists that reach it, starts on 128 bytes and fits before the next one
+        for (uint32_t i = 0; i < ndiag; ++i) {
+            uint32_t live = 0;
+            for (uint32_t l = 0; l < nl; ++l) live += (lists[l] >> 16) > i;
+            if (diag[i] % 8) err = "validate: diagonal alignment";
+            if (diag[i] + live * (uint32_t)lpl > diag[i + 1]) err = "validate: diagonals overlap";
+        }
+        if (nl && ndiag != (lists[0] >> 16)) err = "validate: diagonal count";
+    });
+    if (err) return err;
+    for (uint16_t id : img.stream)
+        if (id > (uint16_t)L.tile_rows) return "validate: row id beyond the zero row";
     return nullptr;
 }
 
@@ -612,7 +674,7 @@ extern "C" int tllm_pack_roundtrip(const int8_t* w, int inners, int columns, con
         info->lanes_per_list = L.lanes_per_list;
         info->nnz = L.nnz;
         info->stream_bytes = (int64_t)img.stream.size() * 2;
-        info->meta_bytes = (int64_t)img.vstart.size() * 4;
+        info->meta_bytes = (int64_t)img.meta.size() * 4;
         info->algorithmic_bytes = 2 * L.nnz + 16 * (int64_t)L.columns * ((L.inners + 511) / 512);
     }
     return TLLM_OK;

@@ -125,6 +125,8 @@ def ter_spmm(X, w_tiled_merged_row_indice, w_tiled_merged_col_offset, w_col_tile
         out = torch.empty((batch_size, rows, columns), device=X.device, dtype=y_dtype)
     elif out.dtype != y_dtype or out.numel() != batch_size * rows * columns or not out.is_contiguous():
         raise RuntimeError("ter_spmm: out has the wrong dtype, size or strides")
+    if batch_size == 0:
+        return out                      # the reference launches nothing for an empty batch (TernaryLinear.py:168)
     tile_ptr = w_col_tile_indices.data_ptr() if w_col_tile_indices is not None and w_col_tile_indices.numel() else None
     with torch.cuda.device(X.device):
         check(lib().tllm_ter_spmm(X.data_ptr(), _lib.torch_dtype_code(X.dtype), layout, w_tiled_merged_row_indice.data_ptr(),

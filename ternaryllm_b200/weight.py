@@ -9,8 +9,8 @@ from . import _lib
 from ._lib import PackOpts, WeightInfo, check, lib, np_ptr
 
 
-def _opts(tile_rows=0, num_ctas=0, lanes_per_list=0, max_rows=0):
-    return PackOpts(int(tile_rows), int(num_ctas), int(lanes_per_list), int(max_rows))
+def _opts(tile_rows=0, num_ctas=0, lanes_per_list=0, max_rows=0, k_splits=0):
+    return PackOpts(int(tile_rows), int(num_ctas), int(lanes_per_list), int(max_rows), int(k_splits))
 
 
 def _dense_i8(w):
