@@ -167,6 +167,22 @@ int tllm_spmm(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows
 int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y, int y_dtype,
                    int y_layout);
 
+/* The same product for callers that are not allowed to allocate device memory -- a serving loop whose
+ * memory budget was fixed at start-up, code living under a framework allocator it must not bypass, a path
+ * where an allocation's implicit synchronisation is unacceptable.  (No counterpart in the reference: its
+ * extension allocates its result on every call, ter_spmm_wrapper.cu:334.)  Inputs and outputs are the
+ * caller's device buffers; the split-K partial sums, arrival counters and status word live in a fixed array
+ * inside the library (about 4 MiB, held by every GPU that loads the library until the process exits) instead
+ * of the scratch the handle got from cudaMalloc.  Nothing is allocated or freed here.
+ *   Limit:  k_splits * min(rows, max_rows) * columns  <=  1 048 576 partial sums, and at most 256 column
+ *           blocks; anything larger is refused with TLLM_ERR_ARG and a message (see tllm_weight_get_info).
+ *   First call on a device looks up the array's device address (once per device, with that device current);
+ *           make that first call outside any stream capture.
+ *   All calls share the one array: the counters and status word are cleared in stream order at every call,
+ *           but two calls that overlap on the GPU (different streams) race and give wrong results. */
+int tllm_spmm_static_scratch(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y,
+                             int y_dtype, void* stream);
+
 /* --------------------------------------------------------------------------------------------------
  * Fused ternary MLP block  y = down( silu(gate(x)) * up(x) )  (TernaryMLP.py:33-35;
  * TernaryMLP<T>::forward, ternaryLLM_CPU/src/LlamaModel.hpp:343-452): gate and up share one activation

@@ -54,6 +54,7 @@ SIGNATURES = {
     "tllm_weight_set_trace": (_I, [_P, _P]),
     "tllm_spmm": (_I, [_P, _P, _I, _I, _I, _P, _I, _P]),
     "tllm_spmm_host": (_I, [_P, _P, _I, _I, _I, _P, _I, _I]),
+    "tllm_spmm_static_scratch": (_I, [_P, _P, _I, _I, _I, _P, _I, _P]),
     "tllm_mlp_create": (_I, [_P, _P, _P, _I, _I, _F, _F, _F, _P, _P]),
     "tllm_mlp_destroy": (_I, [_P]),
     "tllm_mlp_forward": (_I, [_P, _P, _I, _I, _P, _P, _P]),

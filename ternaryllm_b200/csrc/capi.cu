@@ -414,6 +414,119 @@ int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int
     return tllm_weight_check(w);
 }
 
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------------
+// tllm_spmm_static_scratch: the same product as tllm_spmm, for callers that must not allocate.
+//
+// Some callers run where device allocation is off the table: a serving loop whose memory pool was carved up
+// at start-up and is policed for late cudaMalloc calls, code that executes under a framework allocator it
+// must not bypass, or a latency-critical path where an allocation (which may synchronise the device) is not
+// acceptable.  tllm_spmm itself allocates nothing either, but the handle it uses had its split-K scratch
+// allocated with cudaMalloc when it was created.  This entry point does not use that scratch: partial sums,
+// arrival counters and the status word live in the fixed array below, which every GPU that loads this
+// library carries until the process exits.  Its size is the limit on what one call may ask for.
+// ------------------------------------------------------------------------------------------------------
+#define TLLM_STATIC_SCRATCH_CELLS (1u << 20)   // 4-byte partial sums: k_splits * rows_per_launch * columns must fit
+#define TLLM_STATIC_COUNTERS 256u
+#define TLLM_STATIC_SCRATCH_BYTES (TLLM_STATIC_SCRATCH_CELLS * 4u + TLLM_STATIC_COUNTERS * 4u + 256u)
+
+static __device__ __align__(256) unsigned char g_static_scratch[TLLM_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+void* g_static_ptr[64] = {};   // device address of g_static_scratch, per device ordinal
+
+// In host code `g_static_scratch` is only a handle for the runtime, not an address a kernel could use: the
+// device address has to be asked for, once per device, with that device current.
+int static_scratch_address(void** out) {
+    int dev = 0;
+    CU_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(TLLM_ERR_ARG, "tllm_spmm_static_scratch: device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void* ptr = nullptr;
+        CU_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        if (!ptr) return fail(TLLM_ERR_CUDA, "tllm_spmm_static_scratch: cudaGetSymbolAddress returned a null address");
+        g_static_ptr[dev] = ptr;
+    }
+    *out = g_static_ptr[dev];
+    return TLLM_OK;
+}
+}  // namespace
+
+extern "C" int tllm_spmm_static_scratch(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y, int y_dtype,
+                                        void* stream) {
+    if (!w || !X || !Y) return fail(TLLM_ERR_ARG, "tllm_spmm_static_scratch: NULL pointer");
+    if (rows <= 0) return fail(TLLM_ERR_ARG, "tllm_spmm_static_scratch: rows must be positive");
+    if (x_layout != TLLM_ROW_MAJOR && x_layout != TLLM_COL_MAJOR) return fail(TLLM_ERR_ARG, "tllm_spmm_static_scratch: bad x_layout");
+    int rc = check_types(x_dtype, y_dtype, "tllm_spmm_static_scratch");
+    if (rc) return rc;
+    const TsLayout& L = w->lay;
+    const int per_launch = rows < w->max_rows ? rows : w->max_rows;
+    const uint64_t cells = (uint64_t)L.k_splits * (uint64_t)per_launch * (uint64_t)L.columns;
+    if (cells > TLLM_STATIC_SCRATCH_CELLS)
+        return fail(TLLM_ERR_ARG,
+                    "tllm_spmm_static_scratch: %d K-splits x %d rows x %d columns = %llu partial sums exceed the built-in scratch of %u; "
+                    "use tllm_spmm, fewer rows per call, or a weight packed with fewer K-splits",
+                    L.k_splits, per_launch, L.columns, (unsigned long long)cells, (unsigned)TLLM_STATIC_SCRATCH_CELLS);
+    if ((unsigned)L.col_blocks > TLLM_STATIC_COUNTERS) return fail(TLLM_ERR_ARG, "tllm_spmm_static_scratch: too many column blocks for the built-in counters");
+    void* base = nullptr;
+    rc = static_scratch_address(&base);
+    if (rc) return rc;
+    unsigned char* scratch = (unsigned char*)base;
+    unsigned int* counters = (unsigned int*)(scratch + (size_t)TLLM_STATIC_SCRATCH_CELLS * 4u);
+    int* status = (int*)(scratch + (size_t)TLLM_STATIC_SCRATCH_CELLS * 4u + (size_t)TLLM_STATIC_COUNTERS * 4u);
+    cudaStream_t st = (cudaStream_t)stream;
+    // The array keeps whatever the previous call left.  Partial sums are overwritten before they are read;
+    // the counters and the status word must start at zero, so they are cleared here, in stream order.
+    CU_TRY(cudaMemsetAsync(counters, 0, (size_t)TLLM_STATIC_COUNTERS * 4u + 256u, st));
+    const size_t xe = dtype_size(x_dtype), ye = dtype_size(y_dtype);
+    const int x_ld = x_layout == TLLM_ROW_MAJOR ? L.inners : rows;
+    for (int r0 = 0; r0 < rows; r0 += w->max_rows) {
+        const int m = rows - r0 < w->max_rows ? rows - r0 : w->max_rows;
+        const char* xp = (const char*)X + (x_layout == TLLM_ROW_MAJOR ? (size_t)r0 * L.inners : (size_t)r0) * xe;
+        TsParams p{};
+        p.stream = w->d_stream;
+        p.meta = w->d_meta;
+        p.X = xp;
+        p.Y = (char*)Y + (size_t)r0 * L.columns * ye;
+        p.partial = scratch;
+        p.counters = counters;
+        p.status = status;
+        p.trace = nullptr;
+        p.x_dtype = x_dtype;
+        p.x_layout = x_layout;
+        p.y_dtype = y_dtype;
+        p.M = m;
+        p.K = L.inners;
+        p.N = L.columns;
+        p.T = L.tile_rows;
+        p.tiles = L.tiles;
+        p.col_blocks = L.col_blocks;
+        p.cols_per_block = L.cols_per_block;
+        p.sub_cols = L.sub_cols;
+        p.k_splits = L.k_splits;
+        p.tiles_per_cta = L.tiles_per_cta;
+        int lg = 0;
+        while ((1 << lg) < L.lanes_per_list) ++lg;
+        p.lpl_log2 = lg;
+        p.epilogue = 0;
+        p.y_ld = L.columns;
+        p.x_ld = x_ld;
+        p.scale = w->scale;
+        p.scale2 = 0.f;
+        p.x_tma = x_layout == TLLM_ROW_MAJOR && ((uintptr_t)xp % 16 == 0) && ((size_t)x_ld * xe % 16 == 0) && ((size_t)L.tile_rows * xe % 16 == 0) &&
+                  ((size_t)L.inners * xe % 16 == 0);
+        std::memcpy(p.cta, L.cta, sizeof(TsCtaDesc) * (size_t)L.num_ctas);
+        rc = x_dtype == TLLM_I8 ? dispatch_ts<int>(p, L.num_ctas, TS_SMEM_TOTAL, st) : dispatch_ts<float>(p, L.num_ctas, TS_SMEM_TOTAL, st);
+        if (rc) return rc;
+    }
+    return TLLM_OK;
+}
+
+extern "C" {
+
 int tllm_mlp_create(const int8_t* w_gate, const int8_t* w_up, const int8_t* w_down, int hidden, int intermediate, float s_gate,
                     float s_up, float s_down, const tllm_pack_opts* opts, tllm_mlp** out) {
     if (!w_gate || !w_up || !w_down || hidden <= 0 || intermediate <= 0 || !out) return fail(TLLM_ERR_ARG, "tllm_mlp_create: bad argument");
