@@ -85,9 +85,9 @@ struct tllm_mlp {
 
 namespace {
 
-template <typename ACC, int MP, int NW, int D>
+template <typename ACC, int MP, int NW, int D, int NB>
 int launch_ts(const TsParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = tstream_spmm_kernel<ACC, MP, NW, D>;
+    auto kern = tstream_spmm_kernel<ACC, MP, NW, D, NB>;
     static std::mutex mu;
     static bool configured[64] = {};
     int dev = 0;
@@ -118,11 +118,11 @@ template <typename ACC>
 int dispatch_ts(const TsParams& p, int grid, size_t smem, cudaStream_t st) {
     // rows are padded to 1, 2, 4, 8 or 16; up to four rows run 24 warps with two batches of four index vectors
     // per lane, wider tiles trade warps and batch size for registers
-    if (p.M <= 1) return launch_ts<ACC, 1, 24, 4>(p, grid, smem, st);
-    if (p.M <= 2) return launch_ts<ACC, 2, 24, 4>(p, grid, smem, st);
-    if (p.M <= 4) return launch_ts<ACC, 4, 24, 4>(p, grid, smem, st);
-    if (p.M <= 8) return launch_ts<ACC, 8, 16, 2>(p, grid, smem, st);
-    return launch_ts<ACC, 16, 16, 2>(p, grid, smem, st);
+    if (p.M <= 1) return launch_ts<ACC, 1, 24, 4, 2>(p, grid, smem, st);
+    if (p.M <= 2) return launch_ts<ACC, 2, 24, 4, 2>(p, grid, smem, st);
+    if (p.M <= 4) return launch_ts<ACC, 4, 24, 4, 2>(p, grid, smem, st);
+    if (p.M <= 8) return launch_ts<ACC, 8, 16, 2, 2>(p, grid, smem, st);
+    return launch_ts<ACC, 16, 16, 2, 2>(p, grid, smem, st);
 }
 
 int check_types(int x_dtype, int y_dtype, const char* who) {
@@ -169,6 +169,7 @@ int run_ts(tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, i
     p.scale = scale;
     p.scale2 = scale2;
     p.trace = w->d_trace;
+    p.l2_mode = 1;
     std::memcpy(p.cta, L.cta, sizeof(TsCtaDesc) * (size_t)L.num_ctas);
     // bulk-copy staging of the activation tile needs every row segment to start and end on 16 bytes
     const size_t e = dtype_size(x_dtype);
@@ -495,6 +496,7 @@ extern "C" int tllm_spmm_static_scratch(tllm_weight* w, const void* X, int x_dty
         p.counters = counters;
         p.status = status;
         p.trace = nullptr;
+        p.l2_mode = 1;
         p.x_dtype = x_dtype;
         p.x_layout = x_layout;
         p.y_dtype = y_dtype;

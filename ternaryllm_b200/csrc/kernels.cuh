@@ -1,10 +1,10 @@
 // kernels.cuh -- sm_100a device code of libtllm.
 //
-//   tstream_spmm_kernel   the decode product (M = 1..16 rows) on the tile-stream format: one persistent
-//                         thread block per SM; a producer warp pulls the block's contiguous index stream
-//                         through a shared-memory ring with bulk async copies (TMA, mbarrier completion);
-//                         consumer warps gather activations from a bank-replicated shared-memory table,
-//                         so that a warp-wide gather is free of bank conflicts, and add / subtract only.
+//   tstream_spmm_kernel   the decode product (M = 1..16 rows) on the tile-stream format: one thread block
+//                         per SM; the activation tile is staged by TMA bulk copies and expanded into a
+//                         bank-replicated shared-memory table, so that a warp-wide gather is free of bank
+//                         conflicts; each lane streams one sorted index list with 128-bit loads held in
+//                         register batches, gathers, and adds / subtracts only.
 //   mcsc_spmm_kernel      the same product directly on the reference's merged tiled CSC arrays
 //                         (what ter_tiled_mcsc_spmv / ter_tiled_mcsc_spmm compute,
 //                         ternaryLLM_GPU/csrc/ter_spmm_kernel.cuh:24-78, :106-308), for callers that hold
@@ -135,6 +135,7 @@ struct TsParams {
     int epilogue;             // 0: Y = acc*scale ; 1: columns are (gate,up) pairs, Y[c/2] = silu(g*scale)*(u*scale2)
     int y_ld;                 // row stride of Y in elements
     int x_ld;                 // row-major X: elements between rows (K); column-major X: elements between k (total rows)
+    int l2_mode;              // 0: no L2 prefetch of the index range, 1: bulk prefetch by one thread, 2: per-line prefetch by all threads
     int x_tma;                // 1: X is row-major and 16-byte aligned row by row, so tiles of it can be staged by bulk copies
     float scale, scale2;
     TsCtaDesc cta[TS_MAX_CTAS];
@@ -205,6 +206,22 @@ struct Gatherer {
         asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a));
         return bits_as<ACC>(v);
     }
+    // both row ids of one 32-bit word of the stream: the address of each is one 16-bit multiply-add
+    // (id * 128 + lane base) straight from the packed halves, then one load
+    static __device__ __forceinline__ void lds1x2(uint32_t word, uint32_t base, ACC& lo, ACC& hi) {
+        uint32_t x, y;
+        asm volatile(
+            "{\n\t.reg .b16 l, h;\n\t.reg .b32 al, ah;\n\t"
+            "mov.b32 {l, h}, %2;\n\t"
+            "mad.wide.u16 al, l, 128, %3;\n\t"
+            "mad.wide.u16 ah, h, 128, %3;\n\t"
+            "ld.shared.b32 %0, [al];\n\t"
+            "ld.shared.b32 %1, [ah];\n\t}"
+            : "=r"(x), "=r"(y)
+            : "r"(word), "r"(base));
+        lo = bits_as<ACC>(x);
+        hi = bits_as<ACC>(y);
+    }
     static __device__ __forceinline__ P2 lds2(uint32_t a) {
         uint32_t x, y;
         asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(x), "=r"(y) : "r"(a));
@@ -245,10 +262,11 @@ struct Gatherer {
     __device__ __forceinline__ void add8(const uint4& q, ACC (&acc)[MP]) const {
         if (EB == 4) {
             // one accumulator: add the eight gathered values as a tree (depth 4) instead of a chain of 8
-            const ACC v0 = lds1(a1 + (q.x & 0xffffu) * 128u), v1 = lds1(a1 + (q.x >> 16) * 128u);
-            const ACC v2 = lds1(a1 + (q.y & 0xffffu) * 128u), v3 = lds1(a1 + (q.y >> 16) * 128u);
-            const ACC v4 = lds1(a1 + (q.z & 0xffffu) * 128u), v5 = lds1(a1 + (q.z >> 16) * 128u);
-            const ACC v6 = lds1(a1 + (q.w & 0xffffu) * 128u), v7 = lds1(a1 + (q.w >> 16) * 128u);
+            ACC v0, v1, v2, v3, v4, v5, v6, v7;
+            lds1x2(q.x, a1, v0, v1);
+            lds1x2(q.y, a1, v2, v3);
+            lds1x2(q.z, a1, v4, v5);
+            lds1x2(q.w, a1, v6, v7);
             acc[0] += ((v0 + v1) + (v2 + v3)) + ((v4 + v5) + (v6 + v7));
             return;
         }
@@ -362,8 +380,8 @@ __device__ __forceinline__ void fill_row(unsigned char* table, int k, int lane, 
     }
 }
 
-// NW warps, all of them consumers; D index vectors in flight per lane.
-template <typename ACC, int MP, int NW, int D>
+// NW warps; NB register batches of D index vectors per lane (NB-1 batches in flight while one is consumed).
+template <typename ACC, int MP, int NW, int D, int NB>
 __global__ void __launch_bounds__(NW * 32, 1) tstream_spmm_kernel(const __grid_constant__ TsParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int EB = 4 * MP;
@@ -419,21 +437,34 @@ __global__ void __launch_bounds__(NW * 32, 1) tstream_spmm_kernel(const __grid_c
     Gatherer<ACC, MP> gat;
     gat.init(table, lane);
 
-    bool alive = bounded_wait(bar_meta, 0, flags);
-    alive = __all_sync(0xffffffffu, alive);
-    if (!alive && lane == 0) atomicExch(p.status, TS_ERR_META_WAIT);
+    // One warp polls the mbarrier; the others sleep in the hardware barrier instead of spending issue slots
+    // on a polling loop.  The result is published through the abort flag.
+    if (warp == 0) {
+        const bool ok = __all_sync(0xffffffffu, bounded_wait(bar_meta, 0, flags));
+        if (!ok && lane == 0) {
+            flags[0] = 1;
+            atomicExch(p.status, TS_ERR_META_WAIT);
+        }
+    }
+    __syncthreads();
+    bool alive = flags[0] == 0;
     TS_STAMP(2);
 
     // Weights do not depend on the previous kernel.  Pull the block's whole index range towards L2 now (a
     // bounded amount: long ranges are picked up by the loads themselves), and start this warp's first index
     // loads, before waiting for that kernel.
-    if (tid == 0) {
+    {
         const char* g = (const char*)(p.stream + d.stream_off);
         const size_t bytes = min((size_t)d.nvec * 16u, (size_t)TS_L2_PREFETCH_BYTES);
-        for (size_t o = 0; o < bytes; o += 16384) l2_prefetch(g + o, (uint32_t)min((size_t)16384, bytes - o));
+        if (p.l2_mode == 1) {
+            if (tid == 0)
+                for (size_t o = 0; o < bytes; o += 16384) l2_prefetch(g + o, (uint32_t)min((size_t)16384, bytes - o));
+        } else if (p.l2_mode == 2) {
+            for (size_t o = (size_t)tid * 128u; o < bytes; o += (size_t)NT * 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(g + o));
+        }
     }
     const uint4* gstream = p.stream + d.stream_off;
-    uint4 buf[D], buf2[D];
+    uint4 buf[NB][D];
     bool pre = false;
     if (alive) {
         // first section of the block, group `warp`
@@ -447,7 +478,7 @@ __global__ void __launch_bounds__(NW * 32, 1) tstream_spmm_kernel(const __grid_c
             const uint4* ptr = gstream + sec[0] + pos;
 #pragma unroll
             for (int dd = 0; dd < D; ++dd)
-                if (dd < len) buf[dd] = __ldcs(ptr + diag[dd]);
+                if (dd < len) buf[0][dd] = __ldcs(ptr + diag[dd]);
             pre = true;
         }
     }
@@ -479,10 +510,15 @@ __global__ void __launch_bounds__(NW * 32, 1) tstream_spmm_kernel(const __grid_c
                         for (int m = 0; m < p.M; ++m)
                             bulk_g2s(smem_u32(stage) + (uint32_t)m * kc * e, (const char*)p.X + ((size_t)m * p.x_ld + kbase + k0) * e, n * e, bar_x);
                     }
-                    if (alive) {
-                        alive = __all_sync(0xffffffffu, bounded_wait(bar_x, x_phase, flags));
-                        if (!alive && lane == 0) atomicExch(p.status, TS_ERR_X_WAIT);
+                    if (warp == 0 && alive) {
+                        const bool ok = __all_sync(0xffffffffu, bounded_wait(bar_x, x_phase, flags));
+                        if (!ok && lane == 0) {
+                            flags[0] = 1;
+                            atomicExch(p.status, TS_ERR_X_WAIT);
+                        }
                     }
+                    __syncthreads();
+                    alive = flags[0] == 0;
                     x_phase ^= 1u;
                     // one table row (128 bytes) per lane: its 8 chunks are written in an order rotated by the
                     // lane number, so that the 8 lanes of a quarter-warp always write 8 different bank groups
@@ -557,10 +593,10 @@ __global__ void __launch_bounds__(NW * 32, 1) tstream_spmm_kernel(const __grid_c
                 ACC acc[MP];
 #pragma unroll
                 for (int i = 0; i < MP; ++i) acc[i] = 0;
-                // Two register batches of D vectors each.  All loads of a batch are issued back to back, before
-                // the other batch is consumed, so D loads per lane are in flight while the gathers of the other
-                // D run.  (A load issued conditionally inside the loop that consumes its neighbours does not
-                // overlap with them: measured at about half the bandwidth.)
+                // NB register batches of D vectors each.  All loads of a batch are issued back to back, and NB-1
+                // batches are in flight while the gathers of the remaining one run.  (A load issued conditionally
+                // inside the loop that consumes its neighbours does not overlap with them: measured at about
+                // half the bandwidth.)
                 auto load_batch = [&](uint4 (&bf)[D], int base) {
 #pragma unroll
                     for (int dd = 0; dd < D; ++dd)
@@ -571,13 +607,16 @@ __global__ void __launch_bounds__(NW * 32, 1) tstream_spmm_kernel(const __grid_c
                     for (int dd = 0; dd < D; ++dd)
                         if (base + dd < len) gat.add8(bf[dd], acc);
                 };
-                if (!pre) load_batch(buf, 0);
+                if (!pre) load_batch(buf[0], 0);
                 pre = false;
-                for (int i0 = 0; i0 < steps; i0 += 2 * D) {
-                    load_batch(buf2, i0 + D);
-                    use_batch(buf, i0);
-                    load_batch(buf, i0 + 2 * D);
-                    use_batch(buf2, i0 + D);
+#pragma unroll
+                for (int bb = 1; bb < NB - 1; ++bb) load_batch(buf[bb], bb * D);
+                for (int i0 = 0; i0 < steps; i0 += NB * D) {
+#pragma unroll
+                    for (int bb = 0; bb < NB; ++bb) {
+                        load_batch(buf[(bb + NB - 1) % NB], i0 + (bb + NB - 1) * D);
+                        use_batch(buf[bb], i0 + bb * D);
+                    }
                 }
                 gat.unrotate(acc);
                 for (int o = 1; o < lpl; o <<= 1) {   // lanes that share a list
