@@ -40,19 +40,16 @@ NCU_TRAFFIC_BYTES = None
 
 
 def make_weight(seed: int, K: int, N: int, sparsity: float) -> np.ndarray:
+    """Seeded ternary matrix [K, N]: i.i.d. zeros with probability `sparsity` (rounded to a multiple of 1/256),
+    +1 and -1 equiprobable among the rest -- the reference's non-uniform generator (TernaryLinear.py:79-83) with a
+    byte-wide random source, which is what makes generating 10^8 entries take seconds."""
     rng = np.random.default_rng(seed)
-    if abs(sparsity * 256 - round(sparsity * 256)) < 1e-9:
-        z = int(round(sparsity * 256))
-        half = (256 - z) // 2
-        r = rng.integers(0, 256, size=(K, N), dtype=np.uint8)
-        w = np.zeros((K, N), np.int8)
-        w[(r >= z) & (r < z + half)] = -1
-        w[r >= z + half] = 1
-        return w
-    r = rng.random((K, N), dtype=np.float32)
+    z = int(round(sparsity * 256))
+    half = (256 - z) // 2
+    r = rng.integers(0, 256, size=(K, N), dtype=np.uint8)
     w = np.zeros((K, N), np.int8)
-    w[(r >= sparsity) & (r < (sparsity + 1) / 2)] = -1
-    w[r >= (sparsity + 1) / 2] = 1
+    w[(r >= z) & (r < z + half)] = -1
+    w[r >= z + half] = 1
     return w
 
 

@@ -1,0 +1,120 @@
+"""Tensor-parallel sharding logic on two CPU ranks (gloo): column shards concatenate to the full product, row
+shards all-reduce to it.  The packed GPU product is replaced by the oracle's dense product here (tests only);
+the GPU path of the same classes is covered by the decoder benchmark on real devices."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import random_ternary
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _oracle_matmul(x, w_local, scale):
+    import oracle
+
+    y = oracle.dense_f64(x.double().numpy(), w_local, scale)
+    return torch.from_numpy(y)
+
+
+def _worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ternaryllm_b200.tensor_parallel import (ColumnParallelTernaryLinear, RowParallelTernaryLinear, shard_heads,
+                                                     shard_rows)
+
+        rng = np.random.default_rng(5)                     # same weights and activations on every rank
+        K, N, M = 256, 96, 3
+        w1 = random_ternary(rng, K, N, 0.6)
+        w2 = random_ternary(rng, N, K, 0.5)
+        x = torch.from_numpy(rng.integers(-8, 9, size=(M, K)).astype(np.float64))
+        col = ColumnParallelTernaryLinear(w1, world, rank, scale=0.5, matmul=_oracle_matmul)
+        row = RowParallelTernaryLinear(w2, world, rank, scale=2.0, matmul=_oracle_matmul)
+        h_local = col(x)                                    # [M, N/world]
+        gathered = [torch.empty_like(h_local) for _ in range(world)]
+        dist.all_gather(gathered, h_local)
+        h_full = torch.cat(gathered, dim=1)
+        want_h = (x.numpy() @ w1.astype(np.float64)) * 0.5
+        ok = np.array_equal(h_full.numpy(), want_h)
+        y = row(h_local)                                    # consumes the local feature slice, all-reduces
+        want_y = (want_h @ w2.astype(np.float64)) * 2.0
+        ok = ok and np.array_equal(y.numpy(), want_y)
+        # head-wise column shard keeps whole heads
+        wh = shard_heads(w1, 6, 16, world, rank)
+        ok = ok and wh.shape == (K, 96 // world) and np.array_equal(wh, w1[:, rank * 48:(rank + 1) * 48])
+        ok = ok and np.array_equal(shard_rows(w2, world, rank), w2[rank * 48:(rank + 1) * 48])
+        out.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_column_and_row_parallel_on_two_gloo_ranks():
+    world = 2
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(results) == [(0, True), (1, True)]
+
+
+def test_shard_errors():
+    from ternaryllm_b200.tensor_parallel import shard_columns, shard_rows
+
+    w = np.zeros((10, 6), np.int8)
+    with pytest.raises(ValueError):
+        shard_columns(w, 4, 0)
+    with pytest.raises(ValueError):
+        shard_rows(w, 3, 0)
+
+
+@pytest.mark.gpu
+def test_decoder_layer_single_rank_matches_fp32_reference():
+    """One decode step of the Llama-shaped layer (fused QKV, grouped-query attention over a synthetic cache, O,
+    fused MLP) against the same arithmetic in plain fp32 PyTorch on dense weights.  Tolerance 2e-2 relative to the
+    largest output: the layer rounds to bf16 between its stages, the reference does not."""
+    import torch.nn.functional as F
+
+    from bench import make_weight
+    from ternaryllm_b200.tensor_parallel import TernaryDecoderLayerTP, rms_norm
+
+    dev = torch.device("cuda", 0)
+    hidden, ffn, hq, hkv, hd, S, M, L = 1024, 2816, 8, 2, 128, 0.5, 3, 64
+    layer = TernaryDecoderLayerTP(hidden, ffn, hq, hkv, hd, S, 1, 0, dev, kv_len=L, max_batch=4, seed=40, make_weight=make_weight)
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x = torch.randn((M, hidden), generator=g).to(dev, torch.bfloat16)
+    got = layer(x).float()
+    torch.cuda.synchronize()
+
+    def W(i, k, n):
+        return torch.tensor(make_weight(40 + i, k, n, S), dtype=torch.float32, device=dev) * 0.02
+
+    xf = x.float()
+    h = rms_norm(xf)
+    q, k, v = h @ W(1, hidden, hq * hd), h @ W(2, hidden, hkv * hd), h @ W(3, hidden, hkv * hd)
+    kc, vc = layer.k_cache[:M].float().clone(), layer.v_cache[:M].float().clone()
+    kc[:, :, L], vc[:, :, L] = k.view(M, hkv, hd), v.view(M, hkv, hd)
+    a = F.scaled_dot_product_attention(q.view(M, hq, 1, hd), kc.repeat_interleave(hq // hkv, 1), vc.repeat_interleave(hq // hkv, 1))
+    x1 = xf + a.reshape(M, hq * hd) @ W(4, hq * hd, hidden)
+    h2 = rms_norm(x1)
+    want = x1 + (F.silu(h2 @ W(5, hidden, ffn)) * (h2 @ W(6, hidden, ffn))) @ W(7, ffn, hidden)
+    err = (got - want).abs().max().item() / want.abs().max().item()
+    assert err < 2e-2, err
