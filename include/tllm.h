@@ -40,6 +40,14 @@ const char* tllm_last_error(void);
 int tllm_version(void);
 /* number of kernels this library has launched in the calling process (for benchmarks' bookkeeping) */
 int64_t tllm_launch_count(void);
+/* of those, launches of the tensor-core (tcgen05) kernel */
+int64_t tllm_mma_launch_count(void);
+/* Activation rows from which tllm_spmm / tllm_mlp_forward use the tensor-core kernel on the dense two-bit copy
+ * of W instead of the gather kernel on the index lists (fp16 / bf16 row-major activations only; the reference
+ * has one kernel for M = 1 and one for M > 1, ternaryLLM_GPU/csrc/ter_spmm_kernel.cuh:352-372, and no
+ * tensor-core path).  rows = 0 switches the tensor-core kernel off, rows < 0 restores the built-in crossover.
+ * Process-wide; returns the previous value.  The environment variable TLLM_MMA_MIN_ROWS sets the initial value. */
+int tllm_set_mma_min_rows(int rows);
 
 /* --------------------------------------------------------------------------------------------------
  * Host-side packers: the four callables of the reference's `ter_spmm` extension module
@@ -102,7 +110,9 @@ typedef struct tllm_pack_opts {
     int lanes_per_list;   /* lanes that share one index list (power of two, 1..16); 0 = choose from density */
     int max_rows;         /* largest M a single call may pass (scratch is sized for it); 0 = 16 */
     int k_splits;         /* thread blocks that share one column block along K; 0 = choose (1 = no split-K scratch) */
-    int reserved[3];
+    int no_bit_tiles;     /* 1 = do not keep the dense two-bit copy of W that the tensor-core kernel reads (every call
+                             then runs the gather kernel); 0 = keep it (columns*inners/4 bytes) */
+    int reserved[2];
 } tllm_pack_opts;
 
 typedef struct tllm_weight_info {
@@ -113,6 +123,7 @@ typedef struct tllm_weight_info {
     int64_t meta_bytes;        /* list-offset metadata as stored */
     int64_t scratch_bytes;     /* split-K partial sums + counters owned by the handle */
     int64_t algorithmic_bytes; /* 2*nnz + 16*columns*ceil(inners/512): the reference layout's weight bytes */
+    int64_t bit_tile_bytes;    /* dense two-bit copy read by the tensor-core kernel (0 if not kept) */
     float scale;
 } tllm_weight_info;
 

@@ -18,13 +18,13 @@ ROW_MAJOR, COL_MAJOR = 0, 1
 
 class PackOpts(C.Structure):
     _fields_ = [("tile_rows", C.c_int), ("num_ctas", C.c_int), ("lanes_per_list", C.c_int), ("max_rows", C.c_int),
-                ("k_splits", C.c_int), ("reserved", C.c_int * 3)]
+                ("k_splits", C.c_int), ("no_bit_tiles", C.c_int), ("reserved", C.c_int * 2)]
 
 
 class WeightInfo(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("inners", "columns", "tile_rows", "tiles", "col_blocks", "k_splits",
                                        "tiles_per_cta", "num_ctas", "lanes_per_list", "max_rows")] + [
-        (n, C.c_int64) for n in ("nnz", "stream_bytes", "meta_bytes", "scratch_bytes", "algorithmic_bytes")] + [
+        (n, C.c_int64) for n in ("nnz", "stream_bytes", "meta_bytes", "scratch_bytes", "algorithmic_bytes", "bit_tile_bytes")] + [
         ("scale", C.c_float)]
 
     def as_dict(self):
@@ -37,6 +37,8 @@ SIGNATURES = {
     "tllm_last_error": (C.c_char_p, []),
     "tllm_version": (_I, []),
     "tllm_launch_count": (_L, []),
+    "tllm_mma_launch_count": (_L, []),
+    "tllm_set_mma_min_rows": (_I, [_I]),
     "tllm_count_nnz": (_I, [_P, _I, _I, _P, _P]),
     "tllm_convert_to_ter_csc": (_I, [_P, _I, _I, _P, _P, _P, _P]),
     "tllm_convert_to_ter_tiled_csc": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),

@@ -8,7 +8,10 @@
 #include <string>
 #include <vector>
 
+#include <cudaTypedefs.h>
+
 #include "kernels.cuh"
+#include "mma_kernel.cuh"
 #include "util.h"
 
 namespace tllm {
@@ -41,6 +44,22 @@ static size_t dtype_size(int dt) {
     return 0;
 }
 
+// Activation rows from which the tensor-core kernel takes over from the gather kernel (measured crossover on
+// B200; TLLM_MMA_MIN_ROWS overrides it, 0 switches the tensor-core kernel off).
+#define TLLM_MMA_MIN_ROWS_DEFAULT 8
+static std::atomic<int> g_mm_min_rows{-1};
+static std::atomic<int64_t> g_mm_launches{0};
+static int mm_min_rows() {
+    int v = g_mm_min_rows.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char* e = getenv("TLLM_MMA_MIN_ROWS");
+        v = e ? atoi(e) : TLLM_MMA_MIN_ROWS_DEFAULT;
+        if (v < 0) v = TLLM_MMA_MIN_ROWS_DEFAULT;
+        g_mm_min_rows.store(v, std::memory_order_relaxed);
+    }
+    return v == 0 ? (1 << 30) : v;
+}
+
 static bool pdl_enabled() {
     static int v = -1;
     if (v < 0) {
@@ -61,6 +80,7 @@ struct tllm_weight {
     int max_rows = 16;
     uint4* d_stream = nullptr;
     uint32_t* d_meta = nullptr;
+    TsCtaDesc* d_cta = nullptr;
     void* d_partial = nullptr;
     unsigned int* d_counters = nullptr;
     int* d_status = nullptr;
@@ -72,6 +92,12 @@ struct tllm_weight {
     size_t x_cap = 0, y_cap = 0, pin_cap = 0;
     cudaStream_t own_stream = nullptr;
     long long* d_trace = nullptr;   // diagnostics: see tllm_weight_set_trace
+    // tensor-core kernel: dense two-bit copy of W and its split scratch
+    uint4* d_bits = nullptr;
+    float* d_mm_partial = nullptr;
+    unsigned int* d_mm_counters = nullptr;
+    size_t bits_bytes = 0;
+    int mm_n_tiles = 0, mm_kb = 0, mm_grid = 0;
 };
 
 struct tllm_mlp {
@@ -135,6 +161,99 @@ int check_types(int x_dtype, int y_dtype, const char* who) {
     return TLLM_OK;
 }
 
+// ---- tensor-core path -----------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+    });
+    return fn;
+}
+
+// true when the tensor-core kernel can take this call: fp16 / bf16 row-major activations whose rows TMA can address
+bool mm_usable(const tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, int rows) {
+    return w->d_bits && rows >= mm_min_rows() && (x_dtype == TLLM_F16 || x_dtype == TLLM_BF16) && x_layout == TLLM_ROW_MAJOR &&
+           ((uintptr_t)X % 16 == 0) && ((size_t)x_ld * 2 % 16 == 0) && tensor_map_encoder() != nullptr;
+}
+
+// the whole product of `rows` activation rows in one launch of the tensor-core kernel
+int run_mm(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void* Y, int y_dtype, int y_ld, int epilogue, float scale,
+           float scale2, cudaStream_t st) {
+    const TsLayout& L = w->lay;
+    MmParams p{};
+    p.bits = w->d_bits;
+    p.Y = Y;
+    p.partial = w->d_mm_partial;
+    p.counters = w->d_mm_counters;
+    p.status = w->d_status;
+    p.M = rows;
+    p.K = L.inners;
+    p.N = L.columns;
+    p.KB = w->mm_kb;
+    p.n_tiles = w->mm_n_tiles;
+    p.Nt = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
+    p.m_tiles = (rows + p.Nt - 1) / p.Nt;
+    p.y_dtype = y_dtype;
+    p.epilogue = epilogue;
+    p.y_ld = y_ld;
+    p.S = MM_MAX_STAGES;
+    p.R = p.Nt <= 128 ? 4 : 2;
+    p.RAWK = p.Nt <= 128 ? 8 : 4;
+    p.split = p.Nt <= MM_SPLIT_MAX_NT ? 1 : 0;
+    const uint32_t fmt = x_dtype == TLLM_BF16 ? 1u : 0u;
+    // instruction descriptor: fp32 accumulate (bits 4-5 = 1), A and B formats (bits 7-9, 10-12), both K-major,
+    // N / 8 in bits 17-22, M / 16 in bits 24-28
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.Nt >> 3) << 17) | ((uint32_t)(MM_TILE_N >> 4) << 24);
+    p.tmem_cols = 2u * (uint32_t)p.Nt < 32u ? 32u : 2u * (uint32_t)p.Nt;
+    // fp16 holds +-1.0 (0x3C00 / 0xBC00); bf16 holds +-2.0 (0x4000 / 0xC000, whose low byte is zero like fp16's)
+    // and the factor 1/2 moves into the scale
+    p.pool = fmt ? 0x00C04000u : 0x00BC3C00u;
+    p.scale = fmt ? scale * 0.5f : scale;
+    p.scale2 = fmt ? scale2 * 0.5f : scale2;
+
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)L.inners, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)x_ld * 2u};
+    const cuuint32_t box[2] = {MM_TILE_K, (cuuint32_t)p.Nt};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult cr = tensor_map_encoder()(&tmap, fmt ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(X), dims,
+                                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(TLLM_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
+
+    const size_t smem = 1024 + (size_t)p.S * (MM_A_STAGE_BYTES + (size_t)p.Nt * 128) + (size_t)p.R * p.RAWK * MM_CHUNK_BYTES + 256;
+    static std::mutex mu;
+    static bool configured[64] = {};
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (w->device < 64 && !configured[w->device]) {
+            CU_TRY(cudaFuncSetAttribute(mma_spmm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            configured[w->device] = true;
+        }
+    }
+    cudaLaunchConfig_t cfg{};
+    // never more blocks than work items: the hand-over between the blocks that share a tile counts on every
+    // block in a tile's range of owners holding at least one unit of it
+    const long long tiles = (long long)p.n_tiles * p.m_tiles, items = p.split ? tiles * p.KB : tiles;
+    cfg.gridDim = dim3((unsigned)(items < w->mm_grid ? items : w->mm_grid));
+    cfg.blockDim = dim3(MM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    CU_TRY(cudaLaunchKernelEx(&cfg, mma_spmm_kernel, tmap, p));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    g_mm_launches.fetch_add(1, std::memory_order_relaxed);
+    return TLLM_OK;
+}
+
 // one launch of at most max_rows rows
 int run_ts(tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, int rows, void* Y, int y_dtype, int y_ld,
            int epilogue, float scale, float scale2, cudaStream_t st) {
@@ -170,7 +289,8 @@ int run_ts(tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, i
     p.scale2 = scale2;
     p.trace = w->d_trace;
     p.l2_mode = 1;
-    std::memcpy(p.cta, L.cta, sizeof(TsCtaDesc) * (size_t)L.num_ctas);
+    p.cta_ext = w->d_cta;
+    std::memcpy(p.cta, L.cta.data(), sizeof(TsCtaDesc) * (size_t)(L.num_ctas < TS_MAX_CTAS ? L.num_ctas : TS_MAX_CTAS));
     // bulk-copy staging of the activation tile needs every row segment to start and end on 16 bytes
     const size_t e = dtype_size(x_dtype);
     p.x_tma = x_layout == TLLM_ROW_MAJOR && ((uintptr_t)X % 16 == 0) && ((size_t)x_ld * e % 16 == 0) && ((size_t)L.tile_rows * e % 16 == 0) &&
@@ -190,6 +310,8 @@ int upload(tllm_weight* w, const TsHostImage& img, float scale, int max_rows) {
     CU_TRY(cudaMalloc(&w->d_meta, w->meta_bytes + 16));
     CU_TRY(cudaMemcpy(w->d_stream, img.stream.data(), w->stream_bytes, cudaMemcpyHostToDevice));
     CU_TRY(cudaMemcpy(w->d_meta, img.meta.data(), w->meta_bytes, cudaMemcpyHostToDevice));
+    CU_TRY(cudaMalloc(&w->d_cta, img.lay.cta.size() * sizeof(TsCtaDesc)));
+    CU_TRY(cudaMemcpy(w->d_cta, img.lay.cta.data(), img.lay.cta.size() * sizeof(TsCtaDesc), cudaMemcpyHostToDevice));
     const size_t partial_bytes = (size_t)img.lay.k_splits * max_rows * img.lay.columns * 4;
     const size_t counter_bytes = (size_t)img.lay.col_blocks * sizeof(unsigned int);
     w->scratch_bytes = partial_bytes + counter_bytes + sizeof(int);
@@ -198,6 +320,23 @@ int upload(tllm_weight* w, const TsHostImage& img, float scale, int max_rows) {
     CU_TRY(cudaMalloc(&w->d_status, sizeof(int)));
     CU_TRY(cudaMemset(w->d_counters, 0, counter_bytes));
     CU_TRY(cudaMemset(w->d_status, 0, sizeof(int)));
+    CU_TRY(cudaDeviceSynchronize());
+    return TLLM_OK;
+}
+
+int upload_bits(tllm_weight* w, const int8_t* dense, int inners, int columns, int sms) {
+    std::vector<uint32_t> bits;
+    mm_pack_bits(dense, inners, columns, &bits, &w->mm_n_tiles, &w->mm_kb);
+    w->bits_bytes = bits.size() * sizeof(uint32_t);
+    w->mm_grid = sms;
+    CU_TRY(cudaMalloc(&w->d_bits, w->bits_bytes));
+    CU_TRY(cudaMemcpy(w->d_bits, bits.data(), w->bits_bytes, cudaMemcpyHostToDevice));
+    const size_t partial_bytes = (size_t)2 * sms * MM_TILE_N * MM_SPLIT_MAX_NT * sizeof(float);
+    const size_t counter_bytes = (size_t)w->mm_n_tiles * 4 * sizeof(unsigned int);
+    CU_TRY(cudaMalloc(&w->d_mm_partial, partial_bytes));
+    CU_TRY(cudaMalloc(&w->d_mm_counters, counter_bytes));
+    CU_TRY(cudaMemset(w->d_mm_counters, 0, counter_bytes));
+    w->scratch_bytes += partial_bytes + counter_bytes;
     CU_TRY(cudaDeviceSynchronize());
     return TLLM_OK;
 }
@@ -219,7 +358,8 @@ int create_from_dense(const int8_t* dense, int inners, int columns, float scale,
     int max_rows = (opts && opts->max_rows > 0) ? opts->max_rows : 16;
     if (max_rows > 16) max_rows = 16;
     tllm_weight* w = new tllm_weight();
-    const int rc = upload(w, img, scale, max_rows);
+    int rc = upload(w, img, scale, max_rows);
+    if (rc == TLLM_OK && !(opts && opts->no_bit_tiles)) rc = upload_bits(w, dense, inners, columns, sms);
     if (rc != TLLM_OK) {
         tllm_weight_destroy(w);
         return rc;
@@ -250,6 +390,12 @@ extern "C" {
 const char* tllm_last_error(void) { return g_err.c_str(); }
 int tllm_version(void) { return 100; }
 int64_t tllm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+int64_t tllm_mma_launch_count(void) { return g_mm_launches.load(std::memory_order_relaxed); }
+int tllm_set_mma_min_rows(int rows) {
+    const int prev = mm_min_rows();
+    g_mm_min_rows.store(rows < 0 ? TLLM_MMA_MIN_ROWS_DEFAULT : rows, std::memory_order_relaxed);
+    return prev >= (1 << 30) ? 0 : prev;
+}
 
 int tllm_ter_spmm(const void* X, int x_dtype, int x_layout, const int16_t* row_idx, const int32_t* col_off,
                   const int16_t* col_tile_idx, void* Y, int y_dtype, int batch, int rows, int columns,
@@ -306,6 +452,10 @@ int tllm_weight_destroy(tllm_weight* w) {
     if (!w) return TLLM_OK;
     cudaFree(w->d_stream);
     cudaFree(w->d_meta);
+    cudaFree(w->d_cta);
+    cudaFree(w->d_bits);
+    cudaFree(w->d_mm_partial);
+    cudaFree(w->d_mm_counters);
     cudaFree(w->d_partial);
     cudaFree(w->d_counters);
     cudaFree(w->d_status);
@@ -335,6 +485,7 @@ int tllm_weight_get_info(const tllm_weight* w, tllm_weight_info* info) {
     info->meta_bytes = (int64_t)w->meta_bytes;
     info->scratch_bytes = (int64_t)w->scratch_bytes;
     info->algorithmic_bytes = 2 * L.nnz + 16 * (int64_t)L.columns * ((L.inners + 511) / 512);
+    info->bit_tile_bytes = (int64_t)w->bits_bytes;
     info->scale = w->scale;
     return TLLM_OK;
 }
@@ -358,8 +509,9 @@ int tllm_weight_check(tllm_weight* w) {
     if (st != 0) {
         cudaMemset(w->d_status, 0, sizeof(int));
         cudaMemset(w->d_counters, 0, (size_t)w->lay.col_blocks * sizeof(unsigned int));
+        if (w->d_mm_counters) cudaMemset(w->d_mm_counters, 0, (size_t)w->mm_n_tiles * 4 * sizeof(unsigned int));
         return fail(TLLM_ERR_KERNEL, "a bounded wait ran out inside the kernel (code %d: %s)", st,
-                    st == TS_ERR_X_WAIT ? "activation tile never arrived" : "unit table never arrived");
+                    st == MM_ERR_WAIT ? "tensor-core pipeline stalled" : st == TS_ERR_X_WAIT ? "activation tile never arrived" : "unit table never arrived");
     }
     return TLLM_OK;
 }
@@ -373,6 +525,8 @@ int tllm_spmm(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows
     const TsLayout& L = w->lay;
     const size_t xe = dtype_size(x_dtype), ye = dtype_size(y_dtype);
     const int x_ld = x_layout == TLLM_ROW_MAJOR ? L.inners : rows;
+    if (mm_usable(w, X, x_dtype, x_layout, x_ld, rows))
+        return run_mm(w, X, x_dtype, x_ld, rows, Y, y_dtype, L.columns, 0, w->scale, 0.f, (cudaStream_t)stream);
     for (int r0 = 0; r0 < rows; r0 += w->max_rows) {
         const int m = rows - r0 < w->max_rows ? rows - r0 : w->max_rows;
         const char* xp = (const char*)X + (x_layout == TLLM_ROW_MAJOR ? (size_t)r0 * L.inners : (size_t)r0) * xe;
@@ -520,7 +674,8 @@ extern "C" int tllm_spmm_static_scratch(tllm_weight* w, const void* X, int x_dty
         p.scale2 = 0.f;
         p.x_tma = x_layout == TLLM_ROW_MAJOR && ((uintptr_t)xp % 16 == 0) && ((size_t)x_ld * xe % 16 == 0) && ((size_t)L.tile_rows * xe % 16 == 0) &&
                   ((size_t)L.inners * xe % 16 == 0);
-        std::memcpy(p.cta, L.cta, sizeof(TsCtaDesc) * (size_t)L.num_ctas);
+        p.cta_ext = w->d_cta;
+    std::memcpy(p.cta, L.cta.data(), sizeof(TsCtaDesc) * (size_t)(L.num_ctas < TS_MAX_CTAS ? L.num_ctas : TS_MAX_CTAS));
         rc = x_dtype == TLLM_I8 ? dispatch_ts<int>(p, L.num_ctas, TS_SMEM_TOTAL, st) : dispatch_ts<float>(p, L.num_ctas, TS_SMEM_TOTAL, st);
         if (rc) return rc;
     }
@@ -582,6 +737,11 @@ int tllm_mlp_forward(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y,
     char* h = (char*)(H ? H : m->d_h);
     cudaStream_t st = (cudaStream_t)stream;
     const int mr = m->gate_up->max_rows;
+    if (mm_usable(m->gate_up, X, x_dtype, TLLM_ROW_MAJOR, m->hidden, rows) && mm_usable(m->down, h, x_dtype, TLLM_ROW_MAJOR, m->inter, rows)) {
+        int rc = run_mm(m->gate_up, X, x_dtype, m->hidden, rows, h, x_dtype, m->inter, 1, m->s_gate, m->s_up, st);
+        if (rc) return rc;
+        return run_mm(m->down, h, x_dtype, m->inter, rows, Y, x_dtype, m->hidden, 0, m->down->scale, 0.f, st);
+    }
     for (int r0 = 0; r0 < rows; r0 += mr) {
         const int mm = rows - r0 < mr ? rows - r0 : mr;
         int rc = run_ts(m->gate_up, (const char*)X + (size_t)r0 * m->hidden * e, x_dtype, TLLM_ROW_MAJOR, m->hidden, mm,

@@ -138,6 +138,7 @@ struct TsParams {
     int l2_mode;              // 0: no L2 prefetch of the index range, 1: bulk prefetch by one thread, 2: per-line prefetch by all threads
     int x_tma;                // 1: X is row-major and 16-byte aligned row by row, so tiles of it can be staged by bulk copies
     float scale, scale2;
+    const TsCtaDesc* cta_ext;   // all descriptors in device memory; blocks past TS_MAX_CTAS read theirs from here
     TsCtaDesc cta[TS_MAX_CTAS];
 };
 
@@ -393,7 +394,7 @@ __global__ void __launch_bounds__(NW * 32, 1) tstream_spmm_kernel(const __grid_c
     const int warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x;
     const int b = cta % p.col_blocks, j = cta / p.col_blocks;
-    const TsCtaDesc d = p.cta[cta];
+    const TsCtaDesc d = cta < TS_MAX_CTAS ? p.cta[cta] : p.cta_ext[cta];
 
     unsigned char* table = smem + TS_SMEM_TABLE;
     ACC* acc_s = (ACC*)(smem + TS_SMEM_ACC);                   // [MP][sub_cols]

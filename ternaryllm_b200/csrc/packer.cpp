@@ -422,34 +422,34 @@ const char* ts_pack_dense(const int8_t* w, int inners, int columns, const tllm_p
     double best_cost = 1e300;
     for (int tpc = 1; tpc <= tiles; ++tpc) {
         const int splits = (tiles + tpc - 1) / tpc;
-        if (splits > ctas) continue;
         if (o.k_splits > 0 && tpc != (tiles + o.k_splits - 1) / o.k_splits) continue;
-        int nb = std::min(ctas / splits, (columns + 1) / 2);
-        if (nb < 1) nb = 1;
         // column blocks hold an even number of columns, so that (gate, up) column pairs never straddle one
         // (and, when wide enough, a multiple of 16 columns = 32 lists, so that no unit is left with idle lanes)
         auto cols_for = [&](int blocks) {
             const int c = (columns + blocks - 1) / blocks;
             return c >= 64 ? (c + 15) & ~15 : (c + 1) & ~1;
         };
-        int bc = cols_for(nb);
-        // keep the per-block unit table inside its shared-memory budget
-        while (meta_words_of(bc, std::min(bc, TS_MAX_SUB_COLS), T, tpc) * 4 + 16 > TS_MAX_META_BYTES && bc > 2) {
-            ++nb;
-            bc = cols_for(nb);
-        }
-        nb = (columns + bc - 1) / bc;
-        if (nb * splits > TS_MAX_CTAS) continue;
-        // time ~ waves * (work of the busiest block + one activation-table fill per tile it owns)
-        // (a fill takes about as long as streaming the lists of 32 Ki matrix entries at 75 % sparsity)
-        const double waves = (nb * splits + ctas - 1) / ctas;
-        const double work = (double)tpc * bc * T;
-        const double fill = (double)tpc * 32768.0;
-        const double cost = waves * (work + fill);
-        if (cost < best_cost) {
-            best_cost = cost;
-            best_tpc = tpc;
-            best_nb = nb;
+        // one wave of blocks when the per-block section table fits its shared-memory budget; wide matrices
+        // take several full waves instead
+        for (int wv = 1; wv <= 64; ++wv) {
+            int nb = std::min(ctas * wv / splits, (columns + 1) / 2);
+            if (nb < 1) nb = 1;
+            const int bc = cols_for(nb);
+            if (meta_words_of(bc, std::min(bc, TS_MAX_SUB_COLS), T, tpc) * 4 + 16 > TS_MAX_META_BYTES && bc > 2) continue;
+            nb = (columns + bc - 1) / bc;
+            if ((int64_t)nb * splits > TS_MAX_BLOCKS) break;
+            // time ~ waves * (work of the busiest block + one activation-table fill per tile it owns)
+            // (a fill takes about as long as streaming the lists of 32 Ki matrix entries at 75 % sparsity)
+            const double waves = (nb * splits + ctas - 1) / ctas;
+            const double work = (double)tpc * bc * T;
+            const double fill = (double)tpc * 32768.0;
+            const double cost = waves * (work + fill);
+            if (cost < best_cost) {
+                best_cost = cost;
+                best_tpc = tpc;
+                best_nb = nb;
+            }
+            break;   // more waves of smaller blocks only add fills
         }
     }
     if (best_tpc == 0) return "pack: no schedule fits (matrix too wide for the block budget)";
@@ -467,6 +467,7 @@ const char* ts_pack_dense(const int8_t* w, int inners, int columns, const tllm_p
     }
     L.col_blocks = (columns + L.cols_per_block - 1) / L.cols_per_block;
     L.num_ctas = L.col_blocks * L.k_splits;
+    L.cta.assign((size_t)L.num_ctas, TsCtaDesc{});
     L.sub_cols = std::min(L.cols_per_block, TS_MAX_SUB_COLS);
     if (o.lanes_per_list <= 0) {
         // One lane per list keeps padding and shuffles lowest.  Narrow column blocks have too few lists to
@@ -602,7 +603,7 @@ void ts_unpack_dense(const TsHostImage& img, int8_t* w) {
 
 const char* ts_validate(const TsHostImage& img) {
     const TsLayout& L = img.lay;
-    if (L.num_ctas != L.col_blocks * L.k_splits || L.num_ctas > TS_MAX_CTAS) return "validate: block count";
+    if (L.num_ctas != L.col_blocks * L.k_splits || L.num_ctas > TS_MAX_BLOCKS || L.cta.size() != (size_t)L.num_ctas) return "validate: block count";
     if ((L.cols_per_block & 1) || L.sub_cols > TS_MAX_SUB_COLS || L.sub_cols <= 0) return "validate: column block / sub-block size";
     if (L.sub_cols < L.cols_per_block && (L.sub_cols & 1)) return "validate: odd sub-block";
     const int lpl = L.lanes_per_list;
@@ -652,6 +653,41 @@ const char* ts_validate(const TsHostImage& img) {
     return nullptr;
 }
 
+// ---------------------------------------------------------------------------------------------------
+// bit tiles: the dense two-bit copy the tensor-core kernel reads (layout: tstream_format.h)
+// ---------------------------------------------------------------------------------------------------
+void mm_pack_bits(const int8_t* w, int inners, int columns, std::vector<uint32_t>* bits, int* n_tiles, int* kb_out) {
+    const int NT = (columns + 127) / 128, KB = (inners + 63) / 64;
+    bits->assign((size_t)NT * KB * 128 * 4, 0u);
+    for (int kb = 0; kb < KB; ++kb) {
+        const int k1 = std::min(inners, (kb + 1) * 64);
+        for (int k = kb * 64; k < k1; ++k) {
+            const int kl = k - kb * 64, word = kl >> 4, bit = mm_code_bit(kl & 15);
+            const int8_t* row = w + (size_t)k * columns;
+            for (int n = 0; n < columns; ++n) {
+                const int8_t v = row[n];
+                if (!v) continue;
+                const size_t rec = ((size_t)(n >> 7) * KB + kb) * 128 + (n & 127);
+                (*bits)[rec * 4 + word] |= (v > 0 ? 1u : 2u) << bit;
+            }
+        }
+    }
+    *n_tiles = NT;
+    *kb_out = KB;
+}
+
+void mm_unpack_bits(const std::vector<uint32_t>& bits, int inners, int columns, int8_t* w) {
+    const int KB = (inners + 63) / 64;
+    for (int k = 0; k < inners; ++k) {
+        const int kb = k >> 6, kl = k & 63, word = kl >> 4, bit = mm_code_bit(kl & 15);
+        for (int n = 0; n < columns; ++n) {
+            const size_t rec = ((size_t)(n >> 7) * KB + kb) * 128 + (n & 127);
+            const uint32_t c = (bits[rec * 4 + word] >> bit) & 3u;
+            w[(size_t)k * columns + n] = c == 1 ? 1 : c == 2 ? -1 : 0;
+        }
+    }
+}
+
 extern "C" int tllm_pack_roundtrip(const int8_t* w, int inners, int columns, const tllm_pack_opts* opts, int num_sms,
                                    int8_t* w_out, tllm_weight_info* info) {
     if (!w || !w_out || inners <= 0 || columns <= 0 || num_sms <= 0) return tllm::fail(TLLM_ERR_ARG, "tllm_pack_roundtrip: bad argument");
@@ -660,9 +696,20 @@ extern "C" int tllm_pack_roundtrip(const int8_t* w, int inners, int columns, con
     if (!msg) msg = ts_validate(img);
     if (msg) return tllm::fail(TLLM_ERR_ARG, "%s", msg);
     ts_unpack_dense(img, w_out);
+    {   // the second representation must describe the same matrix
+        std::vector<uint32_t> bits;
+        int nt = 0, kb = 0;
+        mm_pack_bits(w, inners, columns, &bits, &nt, &kb);
+        std::vector<int8_t> back((size_t)inners * columns);
+        mm_unpack_bits(bits, inners, columns, back.data());
+        if (std::memcmp(back.data(), w, back.size()) != 0) return tllm::fail(TLLM_ERR_ARG, "bit tiles do not reproduce the matrix");
+        if (info) info->bit_tile_bytes = (int64_t)bits.size() * 4;
+    }
     if (info) {
+        const int64_t keep_bits = info->bit_tile_bytes;
         const TsLayout& L = img.lay;
         std::memset(info, 0, sizeof *info);
+        info->bit_tile_bytes = keep_bits;
         info->inners = L.inners;
         info->columns = L.columns;
         info->tile_rows = L.tile_rows;

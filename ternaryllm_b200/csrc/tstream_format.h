@@ -34,7 +34,9 @@
 #include <cstdint>
 #include <vector>
 
-#define TS_MAX_CTAS 160          // per-block descriptors travel in kernel parameters
+#define TS_MAX_CTAS 160          // resident blocks the schedule is sized for (one per SM); the first TS_MAX_CTAS
+                                 // per-block descriptors travel in kernel parameters, the rest are read from memory
+#define TS_MAX_BLOCKS 4096       // blocks of one launch (wide matrices run as several waves of blocks)
 #define TS_MAX_TILE_ROWS 1024    // (tile_rows+1) rows * 128 B = 128.1 KiB activation table
 #define TS_MAX_SUB_COLS 512      // column sums of a sub-block live in shared memory: 16 rows * 512 * 4 B = 32 KiB
 #define TS_STAGE_BYTES (32 * 1024)   // raw activation tile staged by TMA before it is expanded into the table
@@ -54,11 +56,11 @@ struct TsLayout {
     int tile_rows = 0, tiles = 0;
     int col_blocks = 0, cols_per_block = 0, sub_cols = 0;
     int k_splits = 0, tiles_per_cta = 0;
-    int num_ctas = 0;          // col_blocks * k_splits ; block id = j * col_blocks + b
+    int num_ctas = 0;          // blocks of a launch: col_blocks * k_splits ; block id = j * col_blocks + b
     int lanes_per_list = 0;    // power of two, 1..16
     int64_t nnz = 0;
     int64_t total_vecs = 0;
-    TsCtaDesc cta[TS_MAX_CTAS];
+    std::vector<TsCtaDesc> cta;   // num_ctas descriptors
 };
 
 // number of sub-blocks of a column block of `ncols` columns
@@ -71,6 +73,16 @@ struct TsHostImage {
 };
 
 struct tllm_pack_opts;
+
+// Dense two-bit copy of W for the tensor-core kernel ("bit tiles"): for output-column tile nt (128 columns) and
+// K-slice kb (64 rows), 128 consecutive 16-byte records, one per column, each holding 64 codes
+// (0: zero, 1: +1, 2: -1).  Row k_local of the slice sits in 32-bit word k_local/16 at bit mm_code_bit(k_local%16).
+inline int mm_code_bit(int kk) {            // kk = 0..15
+    const int j = kk >> 1, h = kk & 1;       // output word (two values) and half within it
+    return (j < 4 ? 2 * j : 16 + 2 * (j - 4)) + 8 * h;
+}
+void mm_pack_bits(const int8_t* w, int inners, int columns, std::vector<uint32_t>* bits, int* n_tiles, int* kb);
+void mm_unpack_bits(const std::vector<uint32_t>& bits, int inners, int columns, int8_t* w);
 
 // Builds the image from a dense ternary matrix (int8 [inners][columns]); returns nullptr or an error message.
 const char* ts_pack_dense(const int8_t* w, int inners, int columns, const tllm_pack_opts* opts, int num_sms,

@@ -9,8 +9,8 @@ from . import _lib
 from ._lib import PackOpts, WeightInfo, check, lib, np_ptr
 
 
-def _opts(tile_rows=0, num_ctas=0, lanes_per_list=0, max_rows=0, k_splits=0):
-    return PackOpts(int(tile_rows), int(num_ctas), int(lanes_per_list), int(max_rows), int(k_splits))
+def _opts(tile_rows=0, num_ctas=0, lanes_per_list=0, max_rows=0, k_splits=0, no_bit_tiles=0):
+    return PackOpts(int(tile_rows), int(num_ctas), int(lanes_per_list), int(max_rows), int(k_splits), int(no_bit_tiles))
 
 
 def _dense_i8(w):
@@ -100,11 +100,12 @@ class PackedWeight:
         ydt = torch.int32 if x.dtype == torch.int8 else x.dtype
         if out is None:
             out = torch.empty((rows, info["columns"]), device=x.device, dtype=ydt)
-        elif out.dtype != ydt or tuple(out.shape) != (rows, info["columns"]) or not out.is_contiguous():
+        elif (out.dtype != ydt and not (out.dtype == torch.float32 and ydt != torch.int32)) or \
+                tuple(out.shape) != (rows, info["columns"]) or not out.is_contiguous():
             raise RuntimeError("out has the wrong dtype, shape or strides")
         with torch.cuda.device(x.device):
             check(lib().tllm_spmm(self._h, x.data_ptr(), _lib.torch_dtype_code(x.dtype), _lib.COL_MAJOR if col_major else _lib.ROW_MAJOR,
-                                  rows, out.data_ptr(), _lib.torch_dtype_code(ydt), torch.cuda.current_stream().cuda_stream), "tllm_spmm")
+                                  rows, out.data_ptr(), _lib.torch_dtype_code(out.dtype), torch.cuda.current_stream().cuda_stream), "tllm_spmm")
         return out
 
     def matmul_host(self, x, col_major=False, y_col_major=False):

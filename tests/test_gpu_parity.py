@@ -11,7 +11,7 @@ import torch
 
 import oracle
 from conftest import random_ternary
-from ternaryllm_b200 import PackedMLP, PackedWeight, TernaryLinear, ter_spmm
+from ternaryllm_b200 import PackedMLP, PackedWeight, TernaryLinear, _lib, ter_spmm
 
 pytestmark = pytest.mark.gpu
 
@@ -22,6 +22,16 @@ DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 def dev():
     assert torch.cuda.is_available(), "these tests need a CUDA device"
     return torch.device("cuda", 0)
+
+
+@pytest.fixture(autouse=True)
+def gather_kernel_only():
+    """Everything in this file pins the gather kernel: the tensor-core kernel (tests in test_gpu_tensor_path.py)
+    is switched off for the duration of each test."""
+    L = _lib.lib()
+    prev = L.tllm_set_mma_min_rows(0)
+    yield
+    L.tllm_set_mma_min_rows(prev if prev else -1)
 
 
 def int_acts(rng, M, K, lim, dtype):
@@ -295,6 +305,31 @@ def test_fused_mlp(dtype):
     Z = torch.zeros((3, hidden), dtype=DT[dtype], device=dev())
     assert not mlp.forward(Z).any()
     mlp.close()
+
+
+def test_wide_matrix_runs_as_several_waves_of_blocks():
+    """8192 x 57344 (the fused gate|up width of a 70B-class MLP): the section tables of one wave of blocks would
+    not fit shared memory, so the schedule takes two waves (296 blocks) and the blocks past the first 160 read
+    their descriptors from device memory.  Exact on integer activations, against a dense product on the device."""
+    from bench import make_weight
+
+    K, N = 8192, 57344
+    w = make_weight(3, K, N, 0.875)
+    pw = PackedWeight.from_dense(w, scale=1.0)
+    info = pw.info
+    assert info["num_ctas"] > 160 and info["num_ctas"] == info["col_blocks"] * info["k_splits"]
+    rng = np.random.default_rng(3)
+    Wd = torch.tensor(w, device=dev()).float()
+    for M in (1, 5, 16):
+        xs, X = int_acts(rng, M, K, 8, torch.float32)
+        Y = pw.matmul(X)
+        want = X @ Wd                                      # integer sums far below 2^24: the fp32 GEMM is exact
+        want64 = oracle.dense_f64(xs[:1].astype(np.float64), w, 1.0) if M == 1 else None
+        assert torch.equal(Y, want)
+        if want64 is not None:
+            assert np.array_equal(Y.double().cpu().numpy(), want64)
+    pw.check()
+    pw.close()
 
 
 # ------------------------------------------------------------------------------------------------------
