@@ -200,9 +200,18 @@ int run_mm(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void*
     p.y_dtype = y_dtype;
     p.epilogue = epilogue;
     p.y_ld = y_ld;
-    p.S = MM_MAX_STAGES;
-    p.R = p.Nt <= 128 ? 4 : 2;
-    p.RAWK = p.Nt <= 128 ? 8 : 4;
+    // slices per unit and ring depths: narrow activation tiles take four slices per hand-over and a deep ring of
+    // bit tiles (the stream from HBM is what matters there), wide ones keep the operand ring deep instead
+    p.UK = p.Nt <= 64 ? 4 : 2;
+    p.S = p.Nt == 128 ? 3 : 2;
+    p.R = p.Nt == 64 ? 4 : 8;
+    // (environment overrides for tuning runs: TLLM_MM_UK, TLLM_MM_S, TLLM_MM_R)
+    if (const char* e = getenv("TLLM_MM_UK")) p.UK = atoi(e);
+    if (const char* e = getenv("TLLM_MM_S")) p.S = atoi(e);
+    if (const char* e = getenv("TLLM_MM_R")) p.R = atoi(e);
+    if ((p.UK != 1 && p.UK != 2 && p.UK != 4) || p.S < 1 || p.S > MM_MAX_STAGES || p.R < 1 || p.R > MM_MAX_RAW)
+        return fail(TLLM_ERR_ARG, "tensor-core kernel: bad ring configuration");
+    p.KBU = (p.KB + p.UK - 1) / p.UK;
     p.split = p.Nt <= MM_SPLIT_MAX_NT ? 1 : 0;
     const uint32_t fmt = x_dtype == TLLM_BF16 ? 1u : 0u;
     // instruction descriptor: fp32 accumulate (bits 4-5 = 1), A and B formats (bits 7-9, 10-12), both K-major,
@@ -225,20 +234,23 @@ int run_mm(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void*
                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(TLLM_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
 
-    const size_t smem = 1024 + (size_t)p.S * (MM_A_STAGE_BYTES + (size_t)p.Nt * 128) + (size_t)p.R * p.RAWK * MM_CHUNK_BYTES + 256;
+    const size_t smem = 1024 + (size_t)p.S * p.UK * (MM_A_STAGE_BYTES + (size_t)p.Nt * 128) + (size_t)p.R * p.UK * MM_CHUNK_BYTES + 512;
+    if (smem > 227 * 1024) return fail(TLLM_ERR_ARG, "tensor-core kernel: ring configuration needs %zu bytes of shared memory", smem);
+    void (*kern)(CUtensorMap, MmParams) = p.UK == 4 ? mma_spmm_kernel<4> : p.UK == 2 ? mma_spmm_kernel<2> : mma_spmm_kernel<1>;
     static std::mutex mu;
-    static bool configured[64] = {};
+    static bool configured[64][3] = {};
     {
         std::lock_guard<std::mutex> lk(mu);
-        if (w->device < 64 && !configured[w->device]) {
-            CU_TRY(cudaFuncSetAttribute(mma_spmm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-            configured[w->device] = true;
+        const int slot = p.UK == 4 ? 2 : p.UK == 2 ? 1 : 0;
+        if (w->device < 64 && !configured[w->device][slot]) {
+            CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            configured[w->device][slot] = true;
         }
     }
     cudaLaunchConfig_t cfg{};
     // never more blocks than work items: the hand-over between the blocks that share a tile counts on every
     // block in a tile's range of owners holding at least one unit of it
-    const long long tiles = (long long)p.n_tiles * p.m_tiles, items = p.split ? tiles * p.KB : tiles;
+    const long long tiles = (long long)p.n_tiles * p.m_tiles, items = p.split ? tiles * p.KBU : tiles;
     cfg.gridDim = dim3((unsigned)(items < w->mm_grid ? items : w->mm_grid));
     cfg.blockDim = dim3(MM_THREADS);
     cfg.dynamicSmemBytes = smem;
@@ -248,7 +260,7 @@ int run_mm(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void*
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    CU_TRY(cudaLaunchKernelEx(&cfg, mma_spmm_kernel, tmap, p));
+    CU_TRY(cudaLaunchKernelEx(&cfg, kern, tmap, p));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     g_mm_launches.fetch_add(1, std::memory_order_relaxed);
     return TLLM_OK;

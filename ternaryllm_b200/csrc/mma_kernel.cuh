@@ -14,7 +14,9 @@
 //   warps 2..5    epilogue: tensor memory -> registers -> Y (or split-K partial sums)
 //   warps 6..13   decoders: bit tile -> swizzled fp16 / bf16 tile (two groups of four warps, alternate tiles)
 //   warp 14       loads the activation tiles by TMA
-// Work is the flattened list of (output tile, 64-row slice of K) units.  Up to 64 activation rows the list is
+// Work is the flattened list of (output tile, unit) pairs, a unit being 1, 2 or 4 consecutive 64-row slices of K
+// (more slices per unit for narrow activation tiles, so that the fixed cost of one hand-over between the roles
+// is spread over more bytes).  Up to 64 activation rows the list is
 // cut into equal contiguous ranges, one per block (so every SM streams the same number of bytes); tiles that
 // straddle two or more blocks are summed in block order by the last block to arrive, which makes the result
 // independent of scheduling.  Above 64 rows whole tiles are dealt out and nothing is shared.
@@ -29,11 +31,11 @@
 namespace tllm {
 
 #define MM_TILE_N 128                 // output columns per tile  (the MMA's M)
-#define MM_TILE_K 64                  // rows of W per unit       (four MMAs of K = 16)
+#define MM_TILE_K 64                  // rows of W per slice      (four MMAs of K = 16); a unit is 1, 2 or 4 slices
 #define MM_CHUNK_BYTES 2048           // one bit tile: 128 columns x 16 bytes
 #define MM_A_STAGE_BYTES (MM_TILE_N * MM_TILE_K * 2)
-#define MM_MAX_STAGES 4
-#define MM_MAX_RAW 4
+#define MM_MAX_STAGES 8
+#define MM_MAX_RAW 8
 #define MM_THREADS (15 * 32)
 #define MM_SPLIT_MAX_NT 64            // widest activation tile that may use the equal-range split
 #define MM_ERR_WAIT 3                 // status word: a bounded wait of the tensor-core kernel ran out
@@ -45,12 +47,14 @@ struct MmParams {
     unsigned int* counters;   // [n_tiles][4], zero between launches
     int* status;
     int M, K, N;
-    int KB;                   // ceil(K / 64)
+    int KB;                   // ceil(K / 64): slices
+    int UK;                   // slices per unit: 1, 2 or 4 (the kernel's template argument)
+    int KBU;                  // ceil(KB / UK): units per tile
     int n_tiles, m_tiles;
     int Nt;                   // activation rows per tile (the MMA's N): 16, 32, 64, 128 or 256
     int y_dtype, epilogue, y_ld;
-    int S;                    // operand stages (even)
-    int R, RAWK;              // bit-tile ring: R stages of RAWK tiles
+    int S;                    // operand stages, one unit each
+    int R;                    // bit-tile ring stages, one unit each
     int split;                // 1: equal contiguous unit ranges, 0: whole tiles
     uint32_t idesc;           // tcgen05 instruction descriptor
     uint32_t tmem_cols;       // power of two >= 2 * Nt
@@ -127,37 +131,82 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
     return v;
 }
 
+// Non-blocking probe of a barrier phase: unlike try_wait it never suspends the thread, so a spinning waiter
+// sees the completion within one loop iteration.
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+__device__ __forceinline__ bool bounded_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((it & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > TLLM_WAIT_LIMIT_CLOCKS) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// single-lane roles (producers, MMA issuer) spin on the non-blocking probe; warps that wait with all their
+// lanes use the blocking try_wait of bounded_wait, which parks them instead of spending issue slots
 #define MM_WAIT(bar, par)                                   \
+    do {                                                    \
+        if (!bounded_spin((bar), (par), abort_flag)) goto done; \
+    } while (0)
+#define MM_WAIT_BLOCK(bar, par)                             \
     do {                                                    \
         if (!bounded_wait((bar), (par), abort_flag)) goto done; \
     } while (0)
+// ring position and the parity of its current round
+#define MM_ADVANCE(idx, ph, n) \
+    do {                       \
+        if (++(idx) == (n)) {  \
+            (idx) = 0;         \
+            (ph) ^= 1u;        \
+        }                      \
+    } while (0)
 
+template <int UK>
 __global__ void __launch_bounds__(MM_THREADS, 1) mma_spmm_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ MmParams p) {
     extern __shared__ unsigned char mm_smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // ---- this block's unit range -----------------------------------------------------------------------
-    const long long G = gridDim.x, cta = blockIdx.x, KBl = p.KB;
-    const long long tiles = (long long)p.n_tiles * p.m_tiles, total = tiles * KBl;
-    const long long u0 = p.split ? total * cta / G : (tiles * cta / G) * KBl;
-    const long long u1 = p.split ? total * (cta + 1) / G : (tiles * (cta + 1) / G) * KBl;
+    const long long G = gridDim.x, cta = blockIdx.x, KBU = p.KBU;
+    const long long tiles = (long long)p.n_tiles * p.m_tiles, total = tiles * KBU;
+    const long long u0 = p.split ? total * cta / G : (tiles * cta / G) * KBU;
+    const long long u1 = p.split ? total * (cta + 1) / G : (tiles * (cta + 1) / G) * KBU;
     if (u0 >= u1) return;
 
     // ---- shared memory ---------------------------------------------------------------------------------
     const uint32_t raw0 = smem_u32(mm_smem);
     const uint32_t base = (raw0 + 1023u) & ~1023u;                 // swizzled tiles need 1024-byte alignment
-    const int S = p.S, R = p.R, RAWK = p.RAWK, Nt = p.Nt;
-    const uint32_t b_stage = (uint32_t)Nt * 128u;
-    const uint32_t a_base = base, b_base = a_base + (uint32_t)S * MM_A_STAGE_BYTES, r_base = b_base + (uint32_t)S * b_stage;
-    const uint32_t bar_base = r_base + (uint32_t)(R * RAWK) * MM_CHUNK_BYTES;
-    volatile int* flags = (volatile int*)(mm_smem + (bar_base - raw0) + 8 * 20);   // [0] tensor-memory address, [1] abort
+    const uint32_t S = (uint32_t)p.S, R = (uint32_t)p.R;
+    const int Nt = p.Nt, KB = p.KB;
+    const uint32_t b_slice = (uint32_t)Nt * 128u;
+    const uint32_t a_stage = (uint32_t)UK * MM_A_STAGE_BYTES, b_stage = (uint32_t)UK * b_slice, r_stage = (uint32_t)UK * MM_CHUNK_BYTES;
+    const uint32_t a_base = base, b_base = a_base + S * a_stage, r_base = b_base + S * b_stage;
+    const uint32_t bar_base = r_base + R * r_stage;
+    volatile int* flags = (volatile int*)(mm_smem + (bar_base - raw0) + 8 * 36);   // [0] tensor-memory address, [1] abort
     volatile int* abort_flag = flags + 1;
 #define AB_FULL(s) (bar_base + 8u * (uint32_t)(s))
-#define AB_EMPTY(s) (bar_base + 8u * (4u + (uint32_t)(s)))
-#define RAW_FULL(r) (bar_base + 8u * (8u + (uint32_t)(r)))
-#define RAW_EMPTY(r) (bar_base + 8u * (12u + (uint32_t)(r)))
-#define ACC_FULL(a) (bar_base + 8u * (16u + (uint32_t)(a)))
-#define ACC_EMPTY(a) (bar_base + 8u * (18u + (uint32_t)(a)))
+#define AB_EMPTY(s) (bar_base + 8u * (8u + (uint32_t)(s)))
+#define RAW_FULL(r) (bar_base + 8u * (16u + (uint32_t)(r)))
+#define RAW_EMPTY(r) (bar_base + 8u * (24u + (uint32_t)(r)))
+#define ACC_FULL(a) (bar_base + 8u * (32u + (uint32_t)(a)))
+#define ACC_EMPTY(a) (bar_base + 8u * (34u + (uint32_t)(a)))
 
     if (tid == 0) {
         for (int s = 0; s < MM_MAX_STAGES; ++s) {
@@ -166,7 +215,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_spmm_kernel(const __grid_co
         }
         for (int r = 0; r < MM_MAX_RAW; ++r) {
             mbar_init(RAW_FULL(r), 1);
-            mbar_init(RAW_EMPTY(r), 8);    // all eight decoder warps
+            mbar_init(RAW_EMPTY(r), 4);    // the four decoder warps of the group that took the unit
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(ACC_FULL(a), 1);
@@ -185,126 +234,143 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_spmm_kernel(const __grid_co
     const uint32_t tmem = (uint32_t)flags[0];
     pdl_launch_dependents();
 
+    // Every role walks the same list: segments (tile, units [kbu0, kbu1)) of this block's range.
     if (warp == 0) {
         // ---- bit-tile producer: the weights do not depend on the preceding kernel, so this starts at once
         if (lane == 0) {
-            long long u = u0;
-            uint32_t g = 0;
-            while (u < u1) {
-                const long long tile = u / KBl;
+            uint32_t r = 0, rph = 0;
+            for (long long u = u0; u < u1;) {
+                const long long tile = u / KBU;
                 const int nt = (int)(tile / p.m_tiles);
-                const int kb0 = (int)(u - tile * KBl);
-                const int kb1 = (int)min((long long)p.KB, kb0 + (u1 - u));
-                for (int kb = kb0; kb < kb1; kb += RAWK, ++g) {
-                    const uint32_t r = g % (uint32_t)R;
-                    MM_WAIT(RAW_EMPTY(r), ((g / (uint32_t)R) & 1u) ^ 1u);
-                    const uint32_t bytes = (uint32_t)min(RAWK, kb1 - kb) * MM_CHUNK_BYTES;
+                const int kbu0 = (int)(u - tile * KBU);
+                const int kbu1 = (int)min(KBU, kbu0 + (u1 - u));
+                const uint4* src = p.bits + ((size_t)nt * KB + (size_t)kbu0 * UK) * MM_TILE_N;
+                for (int kbu = kbu0; kbu < kbu1; ++kbu, src += (size_t)UK * MM_TILE_N) {
+                    MM_WAIT(RAW_EMPTY(r), rph ^ 1u);
+                    const uint32_t bytes = (uint32_t)min(UK, KB - kbu * UK) * MM_CHUNK_BYTES;
                     mbar_expect_tx(RAW_FULL(r), bytes);
-                    bulk_g2s(r_base + r * (uint32_t)RAWK * MM_CHUNK_BYTES, p.bits + ((size_t)nt * p.KB + kb) * MM_TILE_N, bytes, RAW_FULL(r));
+                    bulk_g2s(r_base + r * r_stage, src, bytes, RAW_FULL(r));
+                    MM_ADVANCE(r, rph, R);
                 }
-                u += kb1 - kb0;
+                u += kbu1 - kbu0;
             }
         }
     } else if (warp == 14) {
-        // ---- activation-tile producer
+        // ---- activation-tile producer: one TMA box per slice, all slices of a unit on one barrier
         if (lane == 0) {
             pdl_wait();
-            long long u = u0;
-            uint32_t i = 0;
-            while (u < u1) {
-                const long long tile = u / KBl;
-                const int mt = (int)(tile % p.m_tiles);
-                const int kb0 = (int)(u - tile * KBl);
-                const int kb1 = (int)min((long long)p.KB, kb0 + (u1 - u));
-                for (int kb = kb0; kb < kb1; ++kb, ++i) {
-                    const uint32_t s = i % (uint32_t)S;
-                    MM_WAIT(AB_EMPTY(s), ((i / (uint32_t)S) & 1u) ^ 1u);
-                    mbar_expect_tx(AB_FULL(s), b_stage);
-                    tma_load_2d(b_base + s * b_stage, &tmap, kb * MM_TILE_K, mt * Nt, AB_FULL(s));
+            uint32_t s = 0, sph = 0;
+            for (long long u = u0; u < u1;) {
+                const long long tile = u / KBU;
+                const int row0 = (int)(tile % p.m_tiles) * Nt;
+                const int kbu0 = (int)(u - tile * KBU);
+                const int kbu1 = (int)min(KBU, kbu0 + (u1 - u));
+                for (int kbu = kbu0; kbu < kbu1; ++kbu) {
+                    const int nk = min(UK, KB - kbu * UK);
+                    MM_WAIT(AB_EMPTY(s), sph ^ 1u);
+                    mbar_expect_tx(AB_FULL(s), (uint32_t)nk * b_slice);
+                    for (int q = 0; q < nk; ++q)
+                        tma_load_2d(b_base + s * b_stage + (uint32_t)q * b_slice, &tmap, (kbu * UK + q) * MM_TILE_K, row0, AB_FULL(s));
+                    MM_ADVANCE(s, sph, S);
                 }
-                u += kb1 - kb0;
+                u += kbu1 - kbu0;
             }
         }
     } else if (warp == 1) {
         // ---- MMA issuer
         if (lane == 0) {
-            long long u = u0;
-            uint32_t i = 0, j = 0;
-            while (u < u1) {
-                const long long tile = u / KBl;
-                const int kb0 = (int)(u - tile * KBl);
-                const int kb1 = (int)min((long long)p.KB, kb0 + (u1 - u));
-                const uint32_t a = j & 1u;
-                MM_WAIT(ACC_EMPTY(a), ((j >> 1) & 1u) ^ 1u);
+            const uint32_t idesc = p.idesc;
+            const uint64_t ad0 = umma_desc_sw128(a_base), bd0 = umma_desc_sw128(b_base);
+            const uint32_t a_step = a_stage >> 4, b_step = b_stage >> 4, bq_step = b_slice >> 4;
+            uint32_t s = 0, sph = 0, a = 0, aph = 0;
+            for (long long u = u0; u < u1;) {
+                const long long tile = u / KBU;
+                const int kbu0 = (int)(u - tile * KBU);
+                const int kbu1 = (int)min(KBU, kbu0 + (u1 - u));
+                MM_WAIT(ACC_EMPTY(a), aph ^ 1u);
                 tc_fence_after();
                 const uint32_t d = tmem + a * (uint32_t)Nt;
-                for (int kb = kb0; kb < kb1; ++kb, ++i) {
-                    const uint32_t s = i % (uint32_t)S;
-                    MM_WAIT(AB_FULL(s), (i / (uint32_t)S) & 1u);
-                    tc_fence_after();
-                    const uint64_t ad = umma_desc_sw128(a_base + s * MM_A_STAGE_BYTES), bd = umma_desc_sw128(b_base + s * b_stage);
+                uint32_t acc = 0;
+                for (int kbu = kbu0; kbu < kbu1; ++kbu) {
+                    const int nk = min(UK, KB - kbu * UK);
+                    MM_WAIT(AB_FULL(s), sph);
+                    uint64_t ad = ad0 + s * a_step, bd = bd0 + s * b_step;
 #pragma unroll
-                    for (int k4 = 0; k4 < MM_TILE_K / 16; ++k4)      // 16 values = 32 bytes = 2 descriptor address units
-                        umma_f16(d, ad + 2u * k4, bd + 2u * k4, p.idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+                    for (int q = 0; q < UK; ++q, ad += MM_A_STAGE_BYTES >> 4, bd += bq_step) {
+                        if (q < nk) {
+#pragma unroll
+                            for (int k4 = 0; k4 < MM_TILE_K / 16; ++k4) {     // 16 values = 32 bytes = 2 descriptor address units
+                                umma_f16(d, ad + 2u * k4, bd + 2u * k4, idesc, acc);
+                                acc = 1;
+                            }
+                        }
+                    }
                     umma_commit(AB_EMPTY(s));
+                    MM_ADVANCE(s, sph, S);
                 }
                 umma_commit(ACC_FULL(a));
-                ++j;
-                u += kb1 - kb0;
+                a ^= 1u;
+                aph ^= (a == 0);
+                u += kbu1 - kbu0;
             }
         }
     } else if (warp >= 6) {
         // ---- decoders: group 0 (warps 6..9) takes even units, group 1 (warps 10..13) odd units
         const int dw = warp - 6, group = dw >> 2, row = (dw & 3) * 32 + lane;
-        const uint32_t sw = (uint32_t)(row & 7);
-        long long u = u0;
-        uint32_t i = 0, g = 0;
-        while (u < u1) {
-            const long long tile = u / KBl;
-            const int kb0 = (int)(u - tile * KBl);
-            const int kb1 = (int)min((long long)p.KB, kb0 + (u1 - u));
-            for (int kb = kb0; kb < kb1; kb += RAWK, ++g) {
-                const uint32_t r = g % (uint32_t)R;
-                MM_WAIT(RAW_FULL(r), (g / (uint32_t)R) & 1u);
-                const int nk = min(RAWK, kb1 - kb);
-                for (int q = 0; q < nk; ++q, ++i) {
-                    if ((int)(i & 1u) != group) continue;
-                    const uint4 rw = ld_shared_v4(r_base + (r * (uint32_t)RAWK + (uint32_t)q) * MM_CHUNK_BYTES + (uint32_t)row * 16u);
-                    const uint32_t s = i % (uint32_t)S;
-                    MM_WAIT(AB_EMPTY(s), ((i / (uint32_t)S) & 1u) ^ 1u);
-                    const uint32_t arow = a_base + s * MM_A_STAGE_BYTES + (uint32_t)row * 128u;
-                    const uint32_t xs[4] = {rw.x, rw.y, rw.z, rw.w};
+        const uint32_t sw = (uint32_t)(row & 7), pool = p.pool;
+        uint32_t s = 0, sph = 0, r = 0, rph = 0, i = 0;
+        for (long long u = u0; u < u1;) {
+            const long long tile = u / KBU;
+            const int kbu0 = (int)(u - tile * KBU);
+            const int kbu1 = (int)min(KBU, kbu0 + (u1 - u));
+            for (int kbu = kbu0; kbu < kbu1; ++kbu, ++i) {
+                if ((int)(i & 1u) == group) {
+                    const int nk = min(UK, KB - kbu * UK);
+                    MM_WAIT_BLOCK(RAW_FULL(r), rph);
+                    uint4 rw[UK];
 #pragma unroll
-                    for (int w4 = 0; w4 < 4; ++w4) {
-                        uint32_t o[8];
-                        mm_decode_word(xs[w4], p.pool, o);
-                        st_shared_v4(arow + (((uint32_t)(2 * w4) ^ sw) << 4), o[0], o[1], o[2], o[3]);
-                        st_shared_v4(arow + (((uint32_t)(2 * w4 + 1) ^ sw) << 4), o[4], o[5], o[6], o[7]);
+                    for (int q = 0; q < UK; ++q)
+                        if (q < nk) rw[q] = ld_shared_v4(r_base + r * r_stage + (uint32_t)q * MM_CHUNK_BYTES + (uint32_t)row * 16u);
+                    MM_WAIT_BLOCK(AB_EMPTY(s), sph ^ 1u);
+#pragma unroll
+                    for (int q = 0; q < UK; ++q) {
+                        if (q < nk) {
+                            const uint32_t arow = a_base + s * a_stage + (uint32_t)q * MM_A_STAGE_BYTES + (uint32_t)row * 128u;
+                            const uint32_t xs[4] = {rw[q].x, rw[q].y, rw[q].z, rw[q].w};
+#pragma unroll
+                            for (int w4 = 0; w4 < 4; ++w4) {
+                                uint32_t o[8];
+                                mm_decode_word(xs[w4], pool, o);
+                                st_shared_v4(arow + (((uint32_t)(2 * w4) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+                                st_shared_v4(arow + (((uint32_t)(2 * w4 + 1) ^ sw) << 4), o[4], o[5], o[6], o[7]);
+                            }
+                        }
                     }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the tile visible to the tensor core's reads
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the tiles visible to the tensor core's reads
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(AB_FULL(s));
+                    if (lane == 0) {
+                        mbar_arrive(AB_FULL(s));
+                        mbar_arrive(RAW_EMPTY(r));      // the ring stage was read into registers before the decode
+                    }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(RAW_EMPTY(r));
+                MM_ADVANCE(s, sph, S);
+                MM_ADVANCE(r, rph, R);
             }
-            u += kb1 - kb0;
+            u += kbu1 - kbu0;
         }
     } else {
         // ---- epilogue (warps 2..5): a warp may read the 32 tensor-memory lanes selected by warp % 4
         const int q = warp & 3, nl = q * 32 + lane;
         pdl_wait();
-        long long u = u0;
-        uint32_t j = 0;
-        while (u < u1) {
-            const long long tile = u / KBl;
+        uint32_t a = 0, aph = 0;
+        for (long long u = u0; u < u1;) {
+            const long long tile = u / KBU;
             const int nt = (int)(tile / p.m_tiles), mt = (int)(tile % p.m_tiles);
-            const int kb0 = (int)(u - tile * KBl);
-            const int kb1 = (int)min((long long)p.KB, kb0 + (u1 - u));
-            const uint32_t a = j & 1u;
-            MM_WAIT(ACC_FULL(a), (j >> 1) & 1u);
+            const int kbu0 = (int)(u - tile * KBU);
+            const int kbu1 = (int)min(KBU, kbu0 + (u1 - u));
+            MM_WAIT_BLOCK(ACC_FULL(a), aph);
             tc_fence_after();
-            const bool full = kb0 == 0 && kb1 == p.KB;
+            const bool full = kbu0 == 0 && kbu1 == p.KBU;
             const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + a * (uint32_t)Nt;
             float* slot = p.partial + (size_t)(2 * cta + (u == u0 ? 0 : 1)) * (size_t)(MM_TILE_N * Nt);
             const int n = nt * MM_TILE_N + nl;
@@ -319,7 +385,24 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_spmm_kernel(const __grid_co
             for (int c16 = 0; c16 < Nt; c16 += 16) {
                 uint32_t v[16];
                 tmem_ld16(taddr + (uint32_t)c16, v);
-                if (full) {
+                if (full && p.epilogue == 0 && p.y_dtype != TLLM_F32 && !(p.y_ld & 1) && nt * MM_TILE_N + MM_TILE_N <= p.N) {
+                    // 16-bit outputs: neighbouring lanes trade one value per pair of rows, so that every lane
+                    // writes two adjacent columns of one row with a single 4-byte store
+#pragma unroll
+                    for (int t = 0; t < 16; t += 2) {
+                        const float e0 = __uint_as_float(v[t]) * p.scale, e1 = __uint_as_float(v[t + 1]) * p.scale;
+                        const float mine = (lane & 1) ? e1 : e0, send = (lane & 1) ? e0 : e1;
+                        const float got = __shfl_xor_sync(0xffffffffu, send, 1);
+                        const int m = mt * Nt + c16 + t + (lane & 1);
+                        const float lo = (lane & 1) ? got : mine, hi = (lane & 1) ? mine : got;
+                        if (m < p.M) {
+                            uint32_t w;
+                            if (p.y_dtype == TLLM_F16) w = (uint32_t)__half_as_ushort(__float2half_rn(lo)) | ((uint32_t)__half_as_ushort(__float2half_rn(hi)) << 16);
+                            else w = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(lo)) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
+                            *(uint32_t*)((char*)p.Y + ((size_t)m * p.y_ld + (n & ~1)) * 2) = w;
+                        }
+                    }
+                } else if (full) {
 #pragma unroll
                     for (int t = 0; t < 16; ++t) emit(__uint_as_float(v[t]), mt * Nt + c16 + t);
                 } else {
@@ -333,7 +416,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_spmm_kernel(const __grid_co
             if (!full) {
                 // The last of the blocks that share this tile adds their partial sums in block order.  Each
                 // epilogue warp owns 32 output columns of the tile and runs the hand-over for them by itself.
-                const long long first_unit = tile * KBl, last_unit = first_unit + KBl - 1;
+                const long long first_unit = tile * KBU, last_unit = first_unit + KBU - 1;
                 const long long cf = ((first_unit + 1) * G + total - 1) / total - 1, cl = ((last_unit + 1) * G + total - 1) / total - 1;
                 __threadfence();
                 __syncwarp();
@@ -361,8 +444,9 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_spmm_kernel(const __grid_co
                     }
                 }
             }
-            ++j;
-            u += kb1 - kb0;
+            a ^= 1u;
+            aph ^= (a == 0);
+            u += kbu1 - kbu0;
         }
     }
 done:
@@ -382,5 +466,7 @@ done:
 #undef ACC_EMPTY
 }
 #undef MM_WAIT
+#undef MM_WAIT_BLOCK
+#undef MM_ADVANCE
 
 }  // namespace tllm
