@@ -34,9 +34,9 @@ if ROOT not in sys.path:
 K_IN, N_OUT = 4096, 11008
 L2_BYTES = 126 * 1024 * 1024
 METRIC = "ternary_spmv_algorithmic_hbm_gbps"
-# DRAM bytes per launch of the decode kernel from an ncu capture of this workload
-# (dram__bytes_read.sum + dram__bytes_write.sum; see profiles/), or None when no capture has been taken.
-NCU_TRAFFIC_BYTES = None
+# DRAM bytes per launch of the decode kernel from an ncu capture of this workload at one row
+# (dram__bytes_read.sum + dram__bytes_write.sum = 23.70 MB + 0; profiles/tstream_spmm_decode_4096x11008_s75_m1.md).
+NCU_TRAFFIC_BYTES = 23.70e6
 
 
 def make_weight(seed: int, K: int, N: int, sparsity: float) -> np.ndarray:
@@ -113,14 +113,109 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
-def measured_peak():
+def measured_peak(key="hbm_gbs", fallback=6650.0):
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         try:
-            return float(json.load(open(p))["hbm_gbs"]), "measured"
+            return float(json.load(open(p))[key]), "measured"
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return fallback, "fallback"
+
+
+def graph_time_us(torch, fn, reps, warmup=3):
+    """Average time of fn() in microseconds over `reps` replays of a CUDA graph of one call (plain launches if the
+    capture fails), CUDA events on the current stream."""
+    fn()
+    torch.cuda.synchronize()
+    run = fn
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        run = g.replay
+    except Exception:
+        torch.cuda.synchronize()
+    for _ in range(warmup):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def other_configs(torch, device, packed, nnz, K, N, peak_hbm):
+    """Short measurements of the neighbouring configurations (each a few hundred replays): the same weights at
+    4 and 16 rows, the fused MLP block of the same shape at 60 % zeros, and the 13B-shape QKV prefill product on
+    the tensor cores.  Reported beside the headline, not part of it."""
+    from ternaryllm_b200 import PackedMLP, PackedWeight, _lib
+
+    L = _lib.lib()
+    out = []
+    R = len(packed)
+    for M in (4, 16):
+        X = torch.randn((M, K), device=device).to(torch.float16)
+        Y = torch.empty((M, N), dtype=torch.float16, device=device)
+        n0, m0 = L.tllm_launch_count(), L.tllm_mma_launch_count()
+
+        def fn():
+            for w in packed:
+                w.matmul(X, out=Y)
+
+        us = graph_time_us(torch, fn, 50) / R
+        tensor = L.tllm_mma_launch_count() > m0
+        balg = algorithmic_bytes(nnz, K, N, M, 2)
+        out.append({"workload": f"same weights, {M} rows fp16", "kernel": "tensor-core" if tensor else "gather", "us_per_launch": us,
+                    "algorithmic_GBps": balg / us / 1e3, "frac_of_hbm_peak": balg / us / 1e3 / peak_hbm,
+                    "GOPs": M * nnz / us / 1e3})
+    # fused MLP 4096 -> 11008 -> 4096, 60 % zeros, fp16
+    hidden, inter, S = 4096, 11008, 0.6
+    mlps, rng = [], np.random.default_rng(777)
+    for i in range(3):
+        sg, su, sd = (float(np.float16(v)) for v in rng.uniform(0.01, 0.05, 3))
+        mlps.append(PackedMLP(make_weight(50 + 3 * i, hidden, inter, S), make_weight(51 + 3 * i, hidden, inter, S),
+                              make_weight(52 + 3 * i, inter, hidden, S), sg, su, sd, device))
+    infos = mlps[0].info
+    balg_w = sum(i["algorithmic_bytes"] for i in infos)
+    for M in (1, 8, 32):
+        X = torch.randn((M, hidden), device=device).to(torch.float16)
+        Y = torch.empty((M, hidden), dtype=torch.float16, device=device)
+        H = torch.empty((M, inter), dtype=torch.float16, device=device)
+        m0 = L.tllm_mma_launch_count()
+
+        def fn():
+            for m in mlps:
+                m.forward(X, out=Y, h=H)
+
+        us = graph_time_us(torch, fn, 50) / len(mlps)
+        balg = balg_w + 2 * M * 2 * hidden
+        out.append({"workload": f"fused MLP block {hidden}->{inter}->{hidden}, 60% zeros, {M} rows fp16 (two launches)",
+                    "kernel": "tensor-core" if L.tllm_mma_launch_count() > m0 else "gather", "us_per_block": us,
+                    "algorithmic_GBps": balg / us / 1e3, "frac_of_hbm_peak": balg / us / 1e3 / peak_hbm})
+    for m in mlps:
+        m.close()
+    # attention-projection prefill, 13B shape: X [2048, 5120] bf16, W [5120, 15360] at 50 % zeros
+    Kp, Np, Mp = 5120, 15360, 2048
+    wq = PackedWeight.from_dense(make_weight(90, Kp, Np, 0.5), scale=0.02, device=device)
+    X = torch.randn((Mp, Kp), device=device).to(torch.bfloat16)
+    Y = torch.empty((Mp, Np), dtype=torch.bfloat16, device=device)
+    m0 = L.tllm_mma_launch_count()
+    us = graph_time_us(torch, lambda: wq.matmul(X, out=Y), 20)
+    peak_tc, kind = measured_peak("bf16_tflops", 1590.0)
+    tf = 2.0 * Mp * Kp * Np / us / 1e6
+    out.append({"workload": f"QKV prefill, X[{Mp},{Kp}] bf16, W[{Kp},{Np}] 50% zeros", "kernel": "tensor-core" if L.tllm_mma_launch_count() > m0 else "gather",
+                "us_per_launch": us, "dense_equivalent_TFLOPs": tf, "frac_of_bf16_peak": tf / peak_tc, "bf16_peak_TFLOPs": peak_tc, "peak_source": kind})
+    wq.close()
+    return out
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -198,6 +293,9 @@ def main():
     ap.add_argument("--copies", type=int, default=0, help="distinct packed weights per step (0 = enough to exceed 3x L2)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the short measurements of the neighbouring configurations")
+    ap.add_argument("--prefill", action="store_true",
+                    help="time only the 13B-shape QKV prefill product on the tensor cores (X [2048,5120] bf16, W [5120,15360], 50 %% zeros)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
 
@@ -238,6 +336,33 @@ def main():
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=device)
+
+    if a.prefill:
+        Kp, Np, Mp = 5120, 15360, 2048
+        wq = PackedWeight.from_dense(make_weight(90, Kp, Np, 0.5), scale=0.02, device=device)
+        Xp = torch.randn((Mp, Kp), device=device).to(torch.bfloat16)
+        Yp = torch.empty((Mp, Np), dtype=torch.bfloat16, device=device)
+        for _ in range(a.warmup):
+            wq.matmul(Xp, out=Yp)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.steps):
+            wq.matmul(Xp, out=Yp)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / a.steps
+        ref = (Xp[:64].double() @ torch.tensor(make_weight(90, Kp, Np, 0.5), device=device).double()) * 0.02
+        err = float((Yp[:64].double() - ref).abs().max() / ref.abs().max())
+        peak_tc, kind = measured_peak("bf16_tflops", 1590.0)
+        tf = 2.0 * Mp * Kp * Np / us / 1e6
+        print(json.dumps({"metric": "ternary_prefill_dense_equivalent_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": a.steps,
+                          "warmup": a.warmup, "ms_per_step": us / 1e3, "higher_is_better": True, "dtype": "bf16 x ternary, fp32 accumulate",
+                          "data": "synthetic", "config": {"workload": f"QKV prefill, X[{Mp},{Kp}] bf16, W[{Kp},{Np}] 50% zeros", "check_rel_err": err},
+                          "roofline": {"bound": "tensor", "achieved": tf, "peak": peak_tc, "unit": "TFLOP/s", "frac": tf / peak_tc, "peak_source": kind,
+                                       "traffic": None},
+                          "gpu_launches": a.steps}))
+        return 0
 
     peak, peak_kind = measured_peak()
     R = a.copies or max(4, -(-3 * L2_BYTES // (2 * int(K * N * (1 - S)))) + 1)
@@ -362,7 +487,7 @@ def main():
                    "pack": {k: info[k] for k in ("tile_rows", "tiles", "col_blocks", "k_splits", "num_ctas", "lanes_per_list")}},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "frac_physical": (bphys / (us_launch * 1e-6) / 1e9) / peak, "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
-                     "traffic": NCU_TRAFFIC_BYTES},
+                     "traffic": NCU_TRAFFIC_BYTES if (M == 1 and S == 0.75) else None},
         "clocks": clk.summary(),
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": R * 2 * M * K, "d2h_bytes_per_step": R * 2 * M * N,
                 "us_per_call": dt_e2e * 1e6 / R, "steps": e2e_steps},
@@ -375,6 +500,11 @@ def main():
             line["cpu_baseline"] = {"value": balg / dt / 1e9, "unit": "GB/s", "us_per_product": dt * 1e6, **desc}
         except Exception as e:
             line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+    if world == 1 and not a.no_other_configs:
+        try:
+            line["other_configs"] = other_configs(torch, device, packed, nnz, K, N, peak)
+        except Exception as e:
+            line["other_configs"] = [{"failed": str(e)}]
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

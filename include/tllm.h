@@ -42,11 +42,13 @@ int tllm_version(void);
 int64_t tllm_launch_count(void);
 /* of those, launches of the tensor-core (tcgen05) kernel */
 int64_t tllm_mma_launch_count(void);
-/* Activation rows from which tllm_spmm / tllm_mlp_forward use the tensor-core kernel on the dense two-bit copy
- * of W instead of the gather kernel on the index lists (fp16 / bf16 row-major activations only; the reference
- * has one kernel for M = 1 and one for M > 1, ternaryLLM_GPU/csrc/ter_spmm_kernel.cuh:352-372, and no
- * tensor-core path).  rows = 0 switches the tensor-core kernel off, rows < 0 restores the built-in crossover.
- * Process-wide; returns the previous value.  The environment variable TLLM_MMA_MIN_ROWS sets the initial value. */
+/* Which kernel tllm_spmm / tllm_mlp_forward run for fp16 / bf16 row-major activations: the gather kernel on the
+ * index lists, or the tensor-core kernel on the dense two-bit copy of W (the reference has one kernel for M = 1
+ * and one for M > 1, ternaryLLM_GPU/csrc/ter_spmm_kernel.cuh:352-372, and no tensor-core path).
+ *   rows < 0  decide per call from the measured cost model of the two kernels (default; one row always gathers)
+ *   rows = 0  never the tensor-core kernel
+ *   rows > 0  the tensor-core kernel from that many activation rows on
+ * Process-wide; returns the previous setting.  The environment variable TLLM_MMA_MIN_ROWS sets the initial one. */
 int tllm_set_mma_min_rows(int rows);
 
 /* --------------------------------------------------------------------------------------------------

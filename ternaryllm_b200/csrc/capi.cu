@@ -46,18 +46,32 @@ static size_t dtype_size(int dt) {
 
 // Activation rows from which the tensor-core kernel takes over from the gather kernel (measured crossover on
 // B200; TLLM_MMA_MIN_ROWS overrides it, 0 switches the tensor-core kernel off).
-#define TLLM_MMA_MIN_ROWS_DEFAULT 8
-static std::atomic<int> g_mm_min_rows{-1};
+// Which kernel takes a call: -1 = decide per call from a cost model of the two kernels (the default), 0 = never the
+// tensor-core kernel, n > 0 = from n activation rows on.  TLLM_MMA_MIN_ROWS sets the initial value.
+static std::atomic<int> g_mm_min_rows{-2};
 static std::atomic<int64_t> g_mm_launches{0};
 static int mm_min_rows() {
     int v = g_mm_min_rows.load(std::memory_order_relaxed);
-    if (v < 0) {
+    if (v == -2) {
         const char* e = getenv("TLLM_MMA_MIN_ROWS");
-        v = e ? atoi(e) : TLLM_MMA_MIN_ROWS_DEFAULT;
-        if (v < 0) v = TLLM_MMA_MIN_ROWS_DEFAULT;
+        v = e ? atoi(e) : -1;
+        if (v < -1) v = -1;
         g_mm_min_rows.store(v, std::memory_order_relaxed);
     }
-    return v == 0 ? (1 << 30) : v;
+    return v;
+}
+// Cost model measured on B200 (CUDA-graph replays, weights streamed from HBM): the gather kernel costs about
+// 6 us + nnz * g(rows padded to 1, 2, 4, 8, 16) per launch of at most 16 rows, the tensor-core kernel about
+// 9 us + 0.21 ps per matrix entry whatever the row count up to 64.  One row always takes the gather kernel.
+static bool mm_model_prefers_tensor(int64_t nnz, int64_t entries, int rows) {
+    if (rows < 2) return false;
+    static const double g_ps[5] = {0.42, 0.55, 0.76, 1.38, 2.57};
+    const int tail = rows % 16, full = rows / 16;
+    int idx = 0;
+    while ((1 << idx) < tail) ++idx;
+    const double t_gather = full * (6.0 + nnz * g_ps[4] * 1e-6) + (tail ? 6.0 + nnz * g_ps[idx] * 1e-6 : 0.0);
+    const double t_tensor = 9.0 + entries * 0.21e-6 * (rows <= 64 ? 1.0 : rows / 64.0);
+    return t_tensor < t_gather;
 }
 
 static bool pdl_enabled() {
@@ -176,8 +190,13 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
 
 // true when the tensor-core kernel can take this call: fp16 / bf16 row-major activations whose rows TMA can address
 bool mm_usable(const tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, int rows) {
-    return w->d_bits && rows >= mm_min_rows() && (x_dtype == TLLM_F16 || x_dtype == TLLM_BF16) && x_layout == TLLM_ROW_MAJOR &&
-           ((uintptr_t)X % 16 == 0) && ((size_t)x_ld * 2 % 16 == 0) && tensor_map_encoder() != nullptr;
+    if (!w->d_bits || (x_dtype != TLLM_F16 && x_dtype != TLLM_BF16) || x_layout != TLLM_ROW_MAJOR || ((uintptr_t)X % 16) || ((size_t)x_ld * 2 % 16) ||
+        tensor_map_encoder() == nullptr)
+        return false;
+    const int thr = mm_min_rows();
+    if (thr == 0) return false;
+    if (thr > 0) return rows >= thr;
+    return mm_model_prefers_tensor(w->lay.nnz, (int64_t)w->lay.inners * w->lay.columns, rows);
 }
 
 // the whole product of `rows` activation rows in one launch of the tensor-core kernel
@@ -405,8 +424,8 @@ int64_t tllm_launch_count(void) { return g_launches.load(std::memory_order_relax
 int64_t tllm_mma_launch_count(void) { return g_mm_launches.load(std::memory_order_relaxed); }
 int tllm_set_mma_min_rows(int rows) {
     const int prev = mm_min_rows();
-    g_mm_min_rows.store(rows < 0 ? TLLM_MMA_MIN_ROWS_DEFAULT : rows, std::memory_order_relaxed);
-    return prev >= (1 << 30) ? 0 : prev;
+    g_mm_min_rows.store(rows < 0 ? -1 : rows, std::memory_order_relaxed);
+    return prev;
 }
 
 int tllm_ter_spmm(const void* X, int x_dtype, int x_layout, const int16_t* row_idx, const int32_t* col_off,

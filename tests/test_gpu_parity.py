@@ -31,7 +31,7 @@ def gather_kernel_only():
     L = _lib.lib()
     prev = L.tllm_set_mma_min_rows(0)
     yield
-    L.tllm_set_mma_min_rows(prev if prev else -1)
+    L.tllm_set_mma_min_rows(prev)
 
 
 def int_acts(rng, M, K, lim, dtype):

@@ -24,9 +24,10 @@ def dev():
 
 
 @pytest.fixture(autouse=True)
-def default_crossover():
+def tensor_kernel_from_eight_rows():
+    """A fixed crossover, so that which kernel runs does not depend on the cost model (tested on its own below)."""
     L = _lib.lib()
-    prev = L.tllm_set_mma_min_rows(-1)
+    prev = L.tllm_set_mma_min_rows(8)
     yield
     L.tllm_set_mma_min_rows(prev)
 
@@ -79,7 +80,7 @@ def test_tolerance_on_gaussian_activations_and_agreement_with_the_gather_kernel(
         # the gather kernel on the same handle, same inputs: both are within rounding of the fp64 product
         L.tllm_set_mma_min_rows(0)
         Yg = pw.matmul(X)
-        L.tllm_set_mma_min_rows(-1)
+        L.tllm_set_mma_min_rows(8)
         assert mma_launches() == n0 + 1
         assert np.max(np.abs(Yg.double().cpu().numpy() - Y.double().cpu().numpy())) / np.max(np.abs(ref)) <= 2 * eps + 1e-5
     pw.check()
@@ -144,7 +145,7 @@ def test_crossover_setting_and_fallbacks():
     assert prev == 8
     pw.matmul(X.to(torch.float16)[:4].contiguous())
     assert mma_launches() == n0 + 1
-    assert L.tllm_set_mma_min_rows(-1) == 2
+    assert L.tllm_set_mma_min_rows(8) == 2
     lean = PackedWeight.from_dense(w, no_bit_tiles=1)       # no dense copy: always the gather kernel
     assert lean.info["bit_tile_bytes"] == 0
     Y = lean.matmul(X.to(torch.float16))
@@ -152,3 +153,23 @@ def test_crossover_setting_and_fallbacks():
     assert np.array_equal(Y.double().cpu().numpy(), oracle.dense_f64(X.double().cpu().numpy(), w, 1.0))
     pw.close()
     lean.close()
+
+
+def test_cost_model_dispatch():
+    """Default setting: one row always gathers; many rows of a matrix dense enough go to the tensor cores; a
+    90 %-sparse matrix keeps a few rows on the gather kernel (its index lists are shorter than the dense copy)."""
+    L = _lib.lib()
+    L.tllm_set_mma_min_rows(-1)
+    rng = np.random.default_rng(15)
+    K, N = 4096, 2816
+    for s, rows_gather, rows_tensor in ((0.5, (1,), (8, 64, 300)), (0.9, (1, 2, 4), (64, 300))):
+        w = random_ternary(rng, K, N, s)
+        pw = PackedWeight.from_dense(w)
+        for M in rows_gather + rows_tensor:
+            X = torch.tensor(rng.integers(-4, 5, size=(M, K)).astype(np.float32), dtype=torch.bfloat16, device=dev())
+            Y = torch.empty((M, N), dtype=torch.float32, device=dev())
+            n0 = mma_launches()
+            pw.matmul(X, out=Y)
+            assert (mma_launches() - n0 == 1) == (M in rows_tensor), (s, M)
+            assert np.array_equal(Y.double().cpu().numpy(), oracle.dense_f64(X.double().cpu().numpy(), w, 1.0))
+        pw.close()
