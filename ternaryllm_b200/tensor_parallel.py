@@ -103,21 +103,26 @@ class TernaryDecoderLayerTP(nn.Module):
         super().__init__()
         self.hidden, self.ffn, self.hd = hidden, ffn, head_dim
         self.hq, self.hkv = n_heads // world, max(1, n_kv_heads // world)
-        if n_heads % world or (n_kv_heads % world and world % n_kv_heads):
-            raise ValueError("heads do not split over the ranks")
+        if n_heads % world or (n_kv_heads % world and world % n_kv_heads) or ffn % world:
+            raise ValueError("heads or FFN columns do not split over the ranks")
         self.world, self.rank, self.device, self.dtype = world, rank, device, dtype
         mk = make_weight
-        # column-sharded QKV: this rank's query heads, then its key heads, then its value heads, in one packed weight
-        kv_rank = rank * n_kv_heads // world if n_kv_heads >= world else rank // (world // n_kv_heads)
-        wq = mk(seed + 1, hidden, n_heads * head_dim, sparsity)[:, rank * self.hq * head_dim:(rank + 1) * self.hq * head_dim]
-        wk = mk(seed + 2, hidden, n_kv_heads * head_dim, sparsity)[:, kv_rank * head_dim:(kv_rank + self.hkv) * head_dim]
-        wv = mk(seed + 3, hidden, n_kv_heads * head_dim, sparsity)[:, kv_rank * head_dim:(kv_rank + self.hkv) * head_dim]
+        # Every rank draws its own shards directly (independent seeds per matrix and rank): the masks are i.i.d., so a
+        # shard of a big random matrix and a random matrix of the shard's shape are the same thing, and no rank has to
+        # generate the other ranks' entries.  Column-sharded QKV: this rank's query heads, then its key heads, then
+        # its value heads, in one packed weight.  With fewer KV heads than ranks, the ranks that share a KV head
+        # draw it from the same seed.
+        kv_owner = rank if n_kv_heads >= world else rank // (world // n_kv_heads)
+        sd = seed + 1000 * rank
+        wq = mk(sd + 1, hidden, self.hq * head_dim, sparsity)
+        wk = mk(seed + 1000 * kv_owner + 2, hidden, self.hkv * head_dim, sparsity)
+        wv = mk(seed + 1000 * kv_owner + 3, hidden, self.hkv * head_dim, sparsity)
         self.qkv = PackedWeight.from_dense(np.ascontiguousarray(np.concatenate([wq, wk, wv], axis=1)), 0.02, device)
         del wq, wk, wv
-        self.o = PackedWeight.from_dense(shard_rows(mk(seed + 4, n_heads * head_dim, hidden, sparsity), world, rank), 0.02, device)
-        wg = shard_columns(mk(seed + 5, hidden, ffn, sparsity), world, rank)
-        wu = shard_columns(mk(seed + 6, hidden, ffn, sparsity), world, rank)
-        wd = shard_rows(mk(seed + 7, ffn, hidden, sparsity), world, rank)
+        self.o = PackedWeight.from_dense(mk(sd + 4, self.hq * head_dim, hidden, sparsity), 0.02, device)
+        wg = mk(sd + 5, hidden, ffn // world, sparsity)
+        wu = mk(sd + 6, hidden, ffn // world, sparsity)
+        wd = mk(sd + 7, ffn // world, hidden, sparsity)
         self.mlp = PackedMLP(wg, wu, wd, 0.02, 0.02, 0.02, device)
         self.nnz_local = int(self.qkv.info["nnz"] + self.o.info["nnz"] + sum(i["nnz"] for i in self.mlp.info))
         self.alg_bytes_local = int(self.qkv.info["algorithmic_bytes"] + self.o.info["algorithmic_bytes"] +
