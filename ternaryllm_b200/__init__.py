@@ -1,13 +1,17 @@
 """ternaryllm_b200 -- B200-native ternary sparse product Y = X.W.s behind the reference's operator API.
 
 Host side of libtllm.so (C ABI in include/tllm.h): the `ter_spmm` module functions, `TernaryLinear`,
-`LlamaTernaryMLP`, `TernaryConfig`, and the handle wrappers `PackedWeight` / `PackedMLP`.
+`LlamaTernaryMLP`, `LlamaTernaryAttention`, `TernaryConfig`, the handle wrappers `PackedWeight` / `PackedMLP`, and the
+tensor-parallel pieces of `tensor_parallel`.
 """
 from . import ter_spmm
 from .configuration_ternary import TernaryConfig
 from .TernaryLinear import TernaryLinear, convert_ternary_weights, random_ternary_weights
+from .TernaryAttn import LlamaTernaryAttention
 from .TernaryMLP import LlamaTernaryMLP
+from .tensor_parallel import ColumnParallelTernaryLinear, RowParallelTernaryLinear, TernaryDecoderLayerTP
 from .weight import PackedMLP, PackedWeight
 
-__all__ = ["ter_spmm", "TernaryConfig", "TernaryLinear", "LlamaTernaryMLP", "PackedWeight", "PackedMLP",
+__all__ = ["ter_spmm", "TernaryConfig", "TernaryLinear", "LlamaTernaryMLP", "LlamaTernaryAttention", "PackedWeight", "PackedMLP",
+           "ColumnParallelTernaryLinear", "RowParallelTernaryLinear", "TernaryDecoderLayerTP",
            "convert_ternary_weights", "random_ternary_weights"]

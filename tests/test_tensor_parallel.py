@@ -118,3 +118,47 @@ def test_decoder_layer_single_rank_matches_fp32_reference():
     want = x1 + (F.silu(h2 @ W(5, hidden, ffn)) * (h2 @ W(6, hidden, ffn))) @ W(7, ffn, hidden)
     err = (got - want).abs().max().item() / want.abs().max().item()
     assert err < 2e-2, err
+
+
+@pytest.mark.gpu
+def test_attention_projections_fused_qkv_matches_three_products_and_fp32_reference():
+    """LlamaTernaryAttention: one fused q|k|v product against the reference's three separate products
+    (ternaryLLM_GPU/TernaryLLM/TernaryAttn.py:73-75) and against plain fp32 PyTorch on the dense weights;
+    decode with a (k, v) cache and a causal multi-token call.  Tolerance 2e-2 of the largest output (fp16 rounding
+    between the stages)."""
+    import torch.nn.functional as F
+
+    from ternaryllm_b200 import LlamaTernaryAttention, TernaryConfig
+
+    dev = torch.device("cuda", 0)
+    cfg = TernaryConfig(hidden_size=1024, intermediate_size=2816, num_attention_heads=8, num_key_value_heads=2, sparsity=0.6)
+    g = torch.Generator().manual_seed(3)
+    attn = LlamaTernaryAttention(cfg, layer_idx=0, scales=(0.03125,) * 4, generator=g)
+    assert attn.fused_qkv
+    hd, hq, hkv = cfg.head_dim, 8, 2
+    x = torch.randn((2, 5, 1024), generator=g).to(dev, torch.float16)
+    y, _, (k, v) = attn(x, use_cache=True)
+    attn.fused_qkv = False
+    y3, _, _ = attn(x, use_cache=True)
+    attn.fused_qkv = True
+    assert (y.float() - y3.float()).abs().max() <= 2e-3 * y3.float().abs().max()
+
+    W = {n: getattr(attn, n).ternary_weight.to(dev, torch.float32) * 0.03125 for n in ("q_proj", "k_proj", "v_proj", "o_proj")}
+
+    def ref(xf, past=None, causal=True):
+        b, t, _ = xf.shape
+        q = (xf @ W["q_proj"]).view(b, t, hq, hd).transpose(1, 2)
+        kk = (xf @ W["k_proj"]).view(b, t, hkv, hd).transpose(1, 2)
+        vv = (xf @ W["v_proj"]).view(b, t, hkv, hd).transpose(1, 2)
+        if past is not None:
+            kk, vv = torch.cat([past[0], kk], 2), torch.cat([past[1], vv], 2)
+        o = F.scaled_dot_product_attention(q, kk.repeat_interleave(hq // hkv, 1), vv.repeat_interleave(hq // hkv, 1), is_causal=causal and t > 1)
+        return o.transpose(1, 2).reshape(b, t, hq * hd) @ W["o_proj"], (kk, vv)
+
+    want, (kr, vr) = ref(x.float())
+    assert (y.float() - want).abs().max() <= 2e-2 * want.abs().max()
+    # one more token on top of the cache
+    x1 = torch.randn((2, 1, 1024), generator=g).to(dev, torch.float16)
+    y1, _, _ = attn(x1, past_key_value=(k, v), use_cache=True)
+    want1, _ = ref(x1.float(), past=(kr, vr), causal=False)
+    assert (y1.float() - want1).abs().max() <= 2e-2 * want1.abs().max()
