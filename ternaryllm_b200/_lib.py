@@ -62,6 +62,7 @@ SIGNATURES = {
     "tllm_mlp_forward": (_I, [_P, _P, _I, _I, _P, _P, _P]),
     "tllm_mlp_get_info": (_I, [_P, _P, _P]),
     "tllm_silu_mul": (_I, [_P, _P, _I, _L, _P]),
+    "tllm_add_rmsnorm": (_I, [_P, _P, _P, _P, _I, _I, _I, _F, _P]),
 }
 
 _lib = None

@@ -792,6 +792,16 @@ int tllm_mlp_get_info(const tllm_mlp* m, tllm_weight_info* gate_up, tllm_weight_
     return TLLM_OK;
 }
 
+int tllm_add_rmsnorm(void* x, const void* delta, const void* weight, void* h, int dtype, int rows, int hidden, float eps, void* stream) {
+    if (!x || !h || rows < 0 || hidden <= 0) return fail(TLLM_ERR_ARG, "tllm_add_rmsnorm: bad argument");
+    if (dtype != TLLM_F32 && dtype != TLLM_F16 && dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "tllm_add_rmsnorm: unsupported dtype");
+    if (rows == 0) return TLLM_OK;
+    add_rmsnorm_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(x, delta, weight, h, dtype, hidden, eps);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return TLLM_OK;
+}
+
 int tllm_silu_mul(void* g, const void* u, int dtype, int64_t n, void* stream) {
     if (!g || !u || n < 0) return fail(TLLM_ERR_ARG, "tllm_silu_mul: bad argument");
     if (dtype != TLLM_F32 && dtype != TLLM_F16 && dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "tllm_silu_mul: unsupported dtype");

@@ -10,6 +10,8 @@
 //                         ternaryLLM_GPU/csrc/ter_spmm_kernel.cuh:24-78, :106-308), for callers that hold
 //                         those arrays.
 //   silu_mul_kernel       SiLU(g)*u (ternaryLLM_CPU/src/initData.hpp:204-210).
+//   add_rmsnorm_kernel    residual add + RMSNorm between two products of a decoder layer (the reference leaves
+//                         this to stock Hugging Face modules).
 //
 // HBM-bound integer/byte work: no tensor cores here by design.
 #pragma once
@@ -784,6 +786,37 @@ __global__ void silu_mul_kernel(void* g, const void* u, int dtype, long long n) 
     if (i >= n) return;
     const float a = load_act_f32(g, dtype, (size_t)i), bq = load_act_f32(u, dtype, (size_t)i);
     store_out(g, dtype, (size_t)i, silu_mul(a, bq));
+}
+
+// Residual add and RMS normalisation of one row per block, the glue between two ternary products of a decoder
+// layer:  x[r] += delta[r] (when delta is given, rounded once to x's type);  h[r] = x[r] * rsqrt(mean(x[r]^2) + eps)
+// * weight (weight = 1 when absent).  Sums in fp32; x, delta, h and weight share one 16-bit or 32-bit float type.
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(void* x, const void* delta, const void* weight, void* h, int dtype, int hidden, float eps) {
+    __shared__ float red[8];
+    const size_t row = (size_t)blockIdx.x * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += 256) {
+        float v = load_act_f32_cg(x, dtype, row + i);
+        if (delta) {
+            v += load_act_f32_cg(delta, dtype, row + i);
+            v = dtype == TLLM_F32 ? v : dtype == TLLM_F16 ? __half2float(__float2half_rn(v)) : __bfloat162float(__float2bfloat16_rn(v));
+            store_out(x, dtype, row + i, v);
+        }
+        ss += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    const float inv = rsqrtf(tot / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += 256) {
+        const float v = load_act_f32_cg(x, dtype, row + i);
+        const float g = weight ? load_act_f32(weight, dtype, (size_t)i) : 1.f;
+        store_out(h, dtype, row + i, v * inv * g);
+    }
 }
 
 }  // namespace tllm

@@ -16,6 +16,7 @@ import torch
 import torch.distributed as dist
 from torch import nn
 
+from . import _lib
 from .weight import PackedMLP, PackedWeight
 
 
@@ -90,6 +91,20 @@ def rms_norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
     return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
 
 
+def add_rms_norm(x: torch.Tensor, delta, out: torch.Tensor = None, weight: torch.Tensor = None, eps: float = 1e-6) -> torch.Tensor:
+    """One launch: x += delta in place (skipped when delta is None), returns RMSNorm(x) (tllm_add_rmsnorm)."""
+    if x.device.type != "cuda" or not x.is_contiguous() or x.dim() != 2:
+        raise RuntimeError("add_rms_norm expects a contiguous 2-D CUDA tensor")
+    if out is None:
+        out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().tllm_add_rmsnorm(x.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                               weight.data_ptr() if weight is not None else None, out.data_ptr(),
+                                               _lib.torch_dtype_code(x.dtype), x.shape[0], x.shape[1], float(eps),
+                                               torch.cuda.current_stream().cuda_stream), "tllm_add_rmsnorm")
+    return out
+
+
 class TernaryDecoderLayerTP(nn.Module):
     """One Llama-shaped decoder layer for single-token decode with ternary linears, tensor-parallel.
 
@@ -134,9 +149,12 @@ class TernaryDecoderLayerTP(nn.Module):
         self.k_cache = torch.randn((max_batch, self.hkv, kv_len + 1, head_dim), generator=g).to(device, dtype)
         self.v_cache = torch.randn((max_batch, self.hkv, kv_len + 1, head_dim), generator=g).to(device, dtype)
 
-    def forward(self, x):            # x [M, hidden]: one new token per sequence
+    def forward(self, x, delta=None):
+        """x [M, hidden]: the residual stream, one new token per sequence, **updated in place**; delta: the previous
+        layer's MLP output that has not been added yet.  Returns (x, this layer's MLP output still to be added):
+        the add travels with the next RMSNorm, so a layer launches two glue kernels instead of a dozen."""
         M = x.shape[0]
-        h = rms_norm(x)
+        h = add_rms_norm(x, delta)
         qkv = self.qkv.matmul(h)
         q, k, v = qkv.split([self.hq * self.hd, self.hkv * self.hd, self.hkv * self.hd], dim=1)
         q = q.view(M, self.hq, 1, self.hd)
@@ -145,6 +163,6 @@ class TernaryDecoderLayerTP(nn.Module):
         vc[:, :, self.kv_len].copy_(v.view(M, self.hkv, self.hd))
         a = torch.nn.functional.scaled_dot_product_attention(q, kc, vc, enable_gqa=self.hq != self.hkv)
         o = all_reduce_sum(self.o.matmul(a.reshape(M, self.hq * self.hd)))
-        x = x + o
-        y = all_reduce_sum(self.mlp.forward(rms_norm(x)))
-        return x + y
+        h2 = add_rms_norm(x, o)
+        y = all_reduce_sum(self.mlp.forward(h2))
+        return x, y

@@ -101,7 +101,8 @@ def test_decoder_layer_single_rank_matches_fp32_reference():
     layer = TernaryDecoderLayerTP(hidden, ffn, hq, hkv, hd, S, 1, 0, dev, kv_len=L, max_batch=4, seed=40, make_weight=make_weight)
     g = torch.Generator(device="cpu").manual_seed(5)
     x = torch.randn((M, hidden), generator=g).to(dev, torch.bfloat16)
-    got = layer(x).float()
+    xs, delta = layer(x.clone())
+    got = (xs + delta).float()
     torch.cuda.synchronize()
 
     def W(i, k, n):
@@ -113,7 +114,7 @@ def test_decoder_layer_single_rank_matches_fp32_reference():
     kc, vc = layer.k_cache[:M].float().clone(), layer.v_cache[:M].float().clone()
     kc[:, :, L], vc[:, :, L] = k.view(M, hkv, hd), v.view(M, hkv, hd)
     a = F.scaled_dot_product_attention(q.view(M, hq, 1, hd), kc.repeat_interleave(hq // hkv, 1), vc.repeat_interleave(hq // hkv, 1))
-    x1 = xf + a.reshape(M, hq * hd) @ W(4, hq * hd, hidden)
+    x1 = (xf + a.reshape(M, hq * hd) @ W(4, hq * hd, hidden)).bfloat16().float()    # the stream is stored in bf16
     h2 = rms_norm(x1)
     want = x1 + (F.silu(h2 @ W(5, hidden, ffn)) * (h2 @ W(6, hidden, ffn))) @ W(7, ffn, hidden)
     err = (got - want).abs().max().item() / want.abs().max().item()
@@ -162,3 +163,29 @@ def test_attention_projections_fused_qkv_matches_three_products_and_fp32_referen
     y1, _, _ = attn(x1, past_key_value=(k, v), use_cache=True)
     want1, _ = ref(x1.float(), past=(kr, vr), causal=False)
     assert (y1.float() - want1).abs().max() <= 2e-2 * want1.abs().max()
+
+
+@pytest.mark.gpu
+def test_add_rms_norm_matches_pytorch():
+    """tllm_add_rmsnorm against the same arithmetic in PyTorch (fp32 sums, one rounding of the stream, one of the
+    normalised output): the stream must be identical, the output within one unit in the last place."""
+    from ternaryllm_b200.tensor_parallel import add_rms_norm
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(8)
+    for dtype, ulp in ((torch.float32, 2.0 ** -22), (torch.float16, 2.0 ** -10), (torch.bfloat16, 2.0 ** -7)):
+        for rows, hidden in ((1, 8192), (5, 1000), (64, 4096)):
+            x = torch.randn((rows, hidden), generator=g).to(dev, dtype)
+            d = torch.randn((rows, hidden), generator=g).to(dev, dtype)
+            w = (torch.rand((hidden,), generator=g) + 0.5).to(dev, dtype)
+            x2 = x.clone()
+            h = add_rms_norm(x2, d, weight=w)
+            xr = (x.float() + d.float()).to(dtype)
+            assert torch.equal(x2, xr)
+            hr = xr.float() * torch.rsqrt(xr.float().pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+            assert ((h.float() - hr).abs() <= ulp * hr.abs() + 1e-6).all()
+            x3 = x.clone()
+            h0 = add_rms_norm(x3, None)
+            assert torch.equal(x3, x)
+            h0r = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)
+            assert ((h0.float() - h0r).abs() <= ulp * h0r.abs() + 1e-6).all()
