@@ -129,6 +129,13 @@ typedef struct tllm_weight_info {
     float scale;
 } tllm_weight_info;
 
+/* Float weights -> ternary weights and a per-tensor scale, host memory, w and out [inners][columns] row-major
+ * (the reference's ternarize_weights is a stub that raises, ternaryLLM_GPU/TernaryLLM/TernaryLinear.py:19-20).
+ * target_sparsity in (0,1): the round(target_sparsity * n) entries of smallest magnitude become 0; otherwise entries
+ * with |w| <= threshold_factor * mean|w| become 0 (threshold_factor <= 0 means 0.7, the ternary-weight-network rule).
+ * The others become sign(w); *scale = mean |w| of the kept entries (the least-squares scale). */
+int tllm_ternarize(const float* w, int inners, int columns, float threshold_factor, float target_sparsity,
+                   int8_t* out, float* scale);
 /* from a dense ternary matrix, int8 [inners][columns] row-major, host memory */
 int tllm_weight_create_dense(const int8_t* w, int inners, int columns, float scale,
                              const tllm_pack_opts* opts, tllm_weight** out);
@@ -153,6 +160,13 @@ int tllm_pack_roundtrip(const int8_t* w, int inners, int columns, const tllm_pac
                         int8_t* w_out, tllm_weight_info* info);
 int tllm_weight_destroy(tllm_weight* w);
 int tllm_weight_get_info(const tllm_weight* w, tllm_weight_info* info);
+/* Packed-weight files: everything a handle holds on the device (index stream, section tables, block descriptors, the
+ * dense two-bit copy if kept, the scale) in one file, so that a model is packed once and loaded without repacking.
+ * The reference keeps its packed arrays as module buffers in a PyTorch state dict
+ * (ternaryLLM_GPU/TernaryLLM/TernaryLinear.py:144-146); this is the equivalent for handles.  A file written on a
+ * device with another SM count loads and runs (the gather kernel's block schedule is part of the file). */
+int tllm_weight_save(const tllm_weight* w, const char* path);
+int tllm_weight_load(const char* path, tllm_weight** out);
 /* change the per-tensor scale s (host value; takes effect for later calls) */
 int tllm_weight_set_scale(tllm_weight* w, float scale);
 

@@ -294,3 +294,19 @@ def ref_call(family, name, *args):
     r = fn(*conv)
     if r != 0:
         raise KeyError(name)
+
+
+def ternarize_f64(w, sparsity=None, threshold_factor=0.7):
+    """Restatement of the product's float -> ternary rule (tllm_ternarize; the reference's ternarize_weights is a stub,
+    ternaryLLM_GPU/TernaryLLM/TernaryLinear.py:19-20, so parity is unpinned and this numpy version is the definition):
+    zero what is at or below the threshold, sign() for the rest, scale = mean |w| of the kept entries."""
+    w = np.asarray(w, dtype=np.float32)
+    a = np.abs(w).astype(np.float64)
+    if sparsity:
+        k = int(np.rint(np.float64(np.float32(sparsity)) * a.size))
+        thr = -1.0 if k == 0 else np.partition(a.ravel(), k - 1)[k - 1]
+    else:
+        thr = np.float64(np.float32(threshold_factor if threshold_factor > 0 else 0.7)) * (a.sum() / a.size)
+    keep = a > thr
+    t = np.where(keep, np.sign(w), 0).astype(np.int8)
+    return t, (float(a[keep].mean()) if keep.any() else 0.0)

@@ -26,8 +26,15 @@ from .weight import PackedWeight
 MapKSizeToTileSize = {8192: 512, 4096: 512, 3072: 512, 2048: 256, 1024: 256, 512: 64}
 
 
-def ternarize_weights(w: torch.Tensor):
-    raise NotImplementedError("ternarize_weights not implement")   # as in the reference (TernaryLinear.py:19-20)
+def ternarize_weights(w: torch.Tensor, sparsity: float = None, threshold_factor: float = 0.7):
+    """Float weights [in_features, out_features] -> (int32 ternary weights, per-tensor scale).  The reference's function
+    of this name raises NotImplementedError (TernaryLinear.py:19-20); this one applies the threshold rule of ternary
+    weight networks (|w| <= threshold_factor * mean|w| -> 0, or the `sparsity` fraction of smallest magnitudes -> 0;
+    the rest -> sign(w); scale = mean |w| of the kept entries).  Runs on the host (tllm_ternarize)."""
+    from .weight import ternarize
+
+    t, s = ternarize(w, sparsity=sparsity, threshold_factor=threshold_factor)
+    return torch.from_numpy(t.astype(np.int32)), s
 
 
 def random_ternary_weights(size: tuple, sparsity: float = 0.8, uniform: bool = False, block_size: int = 512,
@@ -123,6 +130,13 @@ class TernaryLinear(nn.Module):
             self._packed[idx] = pw
         return pw
 
+    @classmethod
+    def from_float(cls, linear_weight: Tensor, sparsity: float = None, threshold_factor: float = 0.7, **kw):
+        """A TernaryLinear from the weight of an `nn.Linear` ([out_features, in_features], as PyTorch stores it):
+        ternarised with `ternarize_weights`, the per-tensor scale kept in `scale`."""
+        w, s = ternarize_weights(linear_weight.detach().t().contiguous(), sparsity=sparsity, threshold_factor=threshold_factor)
+        return cls(w.shape[0], w.shape[1], weight=w, scale=s, **kw)
+
     def forward(self, input: Tensor) -> Tensor:
         """input: (batch, rows, K) | (batch, K, rows) | (rows, K)  ->  (batch, rows, N) | (rows, N)"""
         assert len(input.shape) <= 3, "Input has dim larger than 3"
@@ -146,4 +160,4 @@ class TernaryLinear(nn.Module):
         return f"in_features={self.in_features}, out_features={self.out_features}, scale={self.scale}, uniform={self.uniform}"
 
 
-__all__ = ["TernaryLinear"]
+__all__ = ["TernaryLinear", "ternarize_weights", "random_ternary_weights", "convert_ternary_weights"]

@@ -6,12 +6,12 @@ tensor-parallel pieces of `tensor_parallel`.
 """
 from . import ter_spmm
 from .configuration_ternary import TernaryConfig
-from .TernaryLinear import TernaryLinear, convert_ternary_weights, random_ternary_weights
+from .TernaryLinear import TernaryLinear, convert_ternary_weights, random_ternary_weights, ternarize_weights
 from .TernaryAttn import LlamaTernaryAttention
 from .TernaryMLP import LlamaTernaryMLP
 from .tensor_parallel import ColumnParallelTernaryLinear, RowParallelTernaryLinear, TernaryDecoderLayerTP
-from .weight import PackedMLP, PackedWeight
+from .weight import PackedMLP, PackedWeight, ternarize
 
 __all__ = ["ter_spmm", "TernaryConfig", "TernaryLinear", "LlamaTernaryMLP", "LlamaTernaryAttention", "PackedWeight", "PackedMLP",
            "ColumnParallelTernaryLinear", "RowParallelTernaryLinear", "TernaryDecoderLayerTP",
-           "convert_ternary_weights", "random_ternary_weights"]
+           "convert_ternary_weights", "random_ternary_weights", "ternarize_weights", "ternarize"]

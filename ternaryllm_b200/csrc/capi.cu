@@ -355,9 +355,15 @@ int upload(tllm_weight* w, const TsHostImage& img, float scale, int max_rows) {
     return TLLM_OK;
 }
 
+int upload_bit_tiles(tllm_weight* w, const std::vector<uint32_t>& bits, int sms);
+
 int upload_bits(tllm_weight* w, const int8_t* dense, int inners, int columns, int sms) {
     std::vector<uint32_t> bits;
     mm_pack_bits(dense, inners, columns, &bits, &w->mm_n_tiles, &w->mm_kb);
+    return upload_bit_tiles(w, bits, sms);
+}
+
+int upload_bit_tiles(tllm_weight* w, const std::vector<uint32_t>& bits, int sms) {
     w->bits_bytes = bits.size() * sizeof(uint32_t);
     w->mm_grid = sms;
     CU_TRY(cudaMalloc(&w->d_bits, w->bits_bytes));
@@ -518,6 +524,96 @@ int tllm_weight_get_info(const tllm_weight* w, tllm_weight_info* info) {
     info->algorithmic_bytes = 2 * L.nnz + 16 * (int64_t)L.columns * ((L.inners + 511) / 512);
     info->bit_tile_bytes = (int64_t)w->bits_bytes;
     info->scale = w->scale;
+    return TLLM_OK;
+}
+
+// ---- packed-weight files: header, block descriptors, index stream, section tables, bit tiles -------------------
+namespace {
+struct WeightFileHeader {
+    char magic[8];                // "TLLMW001"
+    int32_t inners, columns, tile_rows, tiles, col_blocks, cols_per_block, sub_cols, k_splits, tiles_per_cta, num_ctas, lanes_per_list,
+        max_rows, mm_n_tiles, mm_kb;
+    int64_t nnz, total_vecs, stream_elems, meta_words, bits_words;
+    float scale;
+    int32_t reserved[7];
+};
+bool read_exact(FILE* f, void* p, size_t n) { return n == 0 || fread(p, 1, n, f) == n; }
+bool write_exact(FILE* f, const void* p, size_t n) { return n == 0 || fwrite(p, 1, n, f) == n; }
+}  // namespace
+
+int tllm_weight_save(const tllm_weight* w, const char* path) {
+    if (!w || !path) return fail(TLLM_ERR_ARG, "tllm_weight_save: NULL argument");
+    const TsLayout& L = w->lay;
+    WeightFileHeader h{};
+    std::memcpy(h.magic, "TLLMW001", 8);
+    h.inners = L.inners, h.columns = L.columns, h.tile_rows = L.tile_rows, h.tiles = L.tiles, h.col_blocks = L.col_blocks;
+    h.cols_per_block = L.cols_per_block, h.sub_cols = L.sub_cols, h.k_splits = L.k_splits, h.tiles_per_cta = L.tiles_per_cta;
+    h.num_ctas = L.num_ctas, h.lanes_per_list = L.lanes_per_list, h.max_rows = w->max_rows, h.mm_n_tiles = w->mm_n_tiles, h.mm_kb = w->mm_kb;
+    h.nnz = L.nnz, h.total_vecs = L.total_vecs;
+    h.stream_elems = (int64_t)(w->stream_bytes / sizeof(uint16_t)), h.meta_words = (int64_t)(w->meta_bytes / sizeof(uint32_t));
+    h.bits_words = (int64_t)(w->bits_bytes / sizeof(uint32_t));
+    h.scale = w->scale;
+    std::vector<unsigned char> stream(w->stream_bytes), meta(w->meta_bytes), bits(w->bits_bytes);
+    int prev = 0;
+    CU_TRY(cudaGetDevice(&prev));
+    CU_TRY(cudaSetDevice(w->device));
+    CU_TRY(cudaMemcpy(stream.data(), w->d_stream, w->stream_bytes, cudaMemcpyDeviceToHost));
+    CU_TRY(cudaMemcpy(meta.data(), w->d_meta, w->meta_bytes, cudaMemcpyDeviceToHost));
+    if (w->bits_bytes) CU_TRY(cudaMemcpy(bits.data(), w->d_bits, w->bits_bytes, cudaMemcpyDeviceToHost));
+    CU_TRY(cudaSetDevice(prev));
+    FILE* f = fopen(path, "wb");
+    if (!f) return fail(TLLM_ERR_ARG, "tllm_weight_save: cannot open %s for writing", path);
+    const bool ok = write_exact(f, &h, sizeof h) && write_exact(f, L.cta.data(), L.cta.size() * sizeof(TsCtaDesc)) &&
+                    write_exact(f, stream.data(), stream.size()) && write_exact(f, meta.data(), meta.size()) && write_exact(f, bits.data(), bits.size());
+    if (fclose(f) != 0 || !ok) return fail(TLLM_ERR_ARG, "tllm_weight_save: short write to %s", path);
+    return TLLM_OK;
+}
+
+int tllm_weight_load(const char* path, tllm_weight** out) {
+    if (!path || !out) return fail(TLLM_ERR_ARG, "tllm_weight_load: NULL argument");
+    *out = nullptr;
+    FILE* f = fopen(path, "rb");
+    if (!f) return fail(TLLM_ERR_ARG, "tllm_weight_load: cannot open %s", path);
+    WeightFileHeader h{};
+    TsHostImage img;
+    std::vector<uint32_t> bits;
+    bool ok = read_exact(f, &h, sizeof h) && std::memcmp(h.magic, "TLLMW001", 8) == 0;
+    ok = ok && h.num_ctas > 0 && h.num_ctas <= TS_MAX_BLOCKS && h.stream_elems >= 0 && h.meta_words >= 0 && h.bits_words >= 0 &&
+         h.stream_elems < ((int64_t)1 << 40) && h.meta_words < ((int64_t)1 << 34) && h.bits_words < ((int64_t)1 << 38);
+    if (ok) {
+        TsLayout& L = img.lay;
+        L.inners = h.inners, L.columns = h.columns, L.tile_rows = h.tile_rows, L.tiles = h.tiles, L.col_blocks = h.col_blocks;
+        L.cols_per_block = h.cols_per_block, L.sub_cols = h.sub_cols, L.k_splits = h.k_splits, L.tiles_per_cta = h.tiles_per_cta;
+        L.num_ctas = h.num_ctas, L.lanes_per_list = h.lanes_per_list, L.nnz = h.nnz, L.total_vecs = h.total_vecs;
+        L.cta.resize((size_t)h.num_ctas);
+        img.stream.resize((size_t)h.stream_elems);
+        img.meta.resize((size_t)h.meta_words);
+        bits.resize((size_t)h.bits_words);
+        ok = read_exact(f, L.cta.data(), L.cta.size() * sizeof(TsCtaDesc)) && read_exact(f, img.stream.data(), img.stream.size() * sizeof(uint16_t)) &&
+             read_exact(f, img.meta.data(), img.meta.size() * sizeof(uint32_t)) && read_exact(f, bits.data(), bits.size() * sizeof(uint32_t));
+    }
+    fclose(f);
+    if (!ok) return fail(TLLM_ERR_ARG, "tllm_weight_load: %s is not a packed-weight file of this library (or is truncated)", path);
+    if (const char* msg = ts_validate(img)) return fail(TLLM_ERR_ARG, "tllm_weight_load: %s", msg);
+    const int64_t want_bits = (int64_t)((h.columns + 127) / 128) * ((h.inners + 63) / 64) * 128 * 4;
+    if (h.bits_words != 0 && (h.bits_words != want_bits || h.mm_n_tiles != (h.columns + 127) / 128 || h.mm_kb != (h.inners + 63) / 64))
+        return fail(TLLM_ERR_ARG, "tllm_weight_load: bit tiles of %s do not match the matrix shape", path);
+    int dev = 0, sms = 0;
+    CU_TRY(cudaGetDevice(&dev));
+    CU_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (sms > TS_MAX_CTAS) sms = TS_MAX_CTAS;
+    tllm_weight* w = new tllm_weight();
+    int rc = upload(w, img, h.scale, h.max_rows > 0 && h.max_rows <= 16 ? h.max_rows : 16);
+    if (rc == TLLM_OK && h.bits_words) {
+        w->mm_n_tiles = h.mm_n_tiles;
+        w->mm_kb = h.mm_kb;
+        rc = upload_bit_tiles(w, bits, sms);
+    }
+    if (rc != TLLM_OK) {
+        tllm_weight_destroy(w);
+        return rc;
+    }
+    *out = w;
     return TLLM_OK;
 }
 

@@ -5,6 +5,7 @@
 // convert_to_ter_tiled_mcsc, inter_tile_swizzle) and consumes what ternaryLLM_CPU/src/TCSC.hpp:6-409
 // (SparseFormat, MergedTCSC, MergedTCSC_Group) produce.
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <numeric>
@@ -651,6 +652,45 @@ const char* ts_validate(const TsHostImage& img) {
     for (uint16_t id : img.stream)
         if (id > (uint16_t)L.tile_rows) return "validate: row id beyond the zero row";
     return nullptr;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// float weights -> ternary weights + per-tensor scale (the reference's ternarize_weights is a stub that raises,
+// ternaryLLM_GPU/TernaryLLM/TernaryLinear.py:19-20; this is the threshold rule of ternary weight networks)
+// ---------------------------------------------------------------------------------------------------
+extern "C" int tllm_ternarize(const float* w, int inners, int columns, float threshold_factor, float target_sparsity, int8_t* out,
+                              float* scale) {
+    if (!w || !out || inners <= 0 || columns <= 0) return tllm::fail(TLLM_ERR_ARG, "tllm_ternarize: bad argument");
+    if (target_sparsity >= 1.f) return tllm::fail(TLLM_ERR_ARG, "tllm_ternarize: target_sparsity must be below 1");
+    const size_t n = (size_t)inners * columns;
+    double thr;
+    if (target_sparsity > 0.f) {
+        // zero the k smallest magnitudes: the threshold is the k-th smallest |w| (ties at the threshold are zeroed too)
+        const size_t k = (size_t)std::llround((double)target_sparsity * (double)n);
+        if (k == 0) thr = -1.0;
+        else {
+            std::vector<float> mag(n);
+            for (size_t i = 0; i < n; ++i) mag[i] = std::fabs(w[i]);
+            std::nth_element(mag.begin(), mag.begin() + (k - 1), mag.end());
+            thr = mag[k - 1];
+        }
+    } else {
+        double sum = 0.0;
+        for (size_t i = 0; i < n; ++i) sum += std::fabs((double)w[i]);
+        thr = (double)(threshold_factor > 0.f ? threshold_factor : 0.7f) * (sum / (double)n);
+    }
+    double kept = 0.0;
+    size_t cnt = 0;
+    for (size_t i = 0; i < n; ++i) {
+        const double a = std::fabs((double)w[i]);
+        if (a > thr) {
+            out[i] = w[i] > 0.f ? 1 : -1;
+            kept += a;
+            ++cnt;
+        } else out[i] = 0;
+    }
+    if (scale) *scale = cnt ? (float)(kept / (double)cnt) : 0.f;     // least-squares scale for the kept entries
+    return TLLM_OK;
 }
 
 // ---------------------------------------------------------------------------------------------------

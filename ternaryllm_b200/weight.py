@@ -71,6 +71,20 @@ class PackedWeight:
             check(fn(o, h), "PackedWeight")
         return cls(h, dev.index if dev.index is not None else torch.cuda.current_device())
 
+    @classmethod
+    def load(cls, path, device=None):
+        """A handle from a file written by `save` (no repacking)."""
+        import torch
+
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        h = C.c_void_p()
+        with torch.cuda.device(dev):
+            check(lib().tllm_weight_load(str(path).encode(), C.byref(h)), "PackedWeight.load")
+        return cls(h, dev.index if dev.index is not None else torch.cuda.current_device())
+
+    def save(self, path):
+        check(lib().tllm_weight_save(self._h, str(path).encode()), "PackedWeight.save")
+
     # ---- use ---------------------------------------------------------------------------------------
     @property
     def info(self):
@@ -134,6 +148,20 @@ class PackedWeight:
             self.close()
         except Exception:
             pass
+
+
+def ternarize(w, sparsity=None, threshold_factor=0.7):
+    """Float weights [inners, columns] -> (int8 ternary weights, per-tensor scale); see tllm_ternarize."""
+    if hasattr(w, "detach"):
+        w = w.detach().float().cpu().numpy()
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    if w.ndim != 2:
+        raise ValueError("ternarize expects a 2-D weight")
+    out = np.empty(w.shape, np.int8)
+    scale = C.c_float()
+    check(lib().tllm_ternarize(np_ptr(w), w.shape[0], w.shape[1], float(threshold_factor), float(sparsity or 0.0), np_ptr(out), C.byref(scale)),
+          "tllm_ternarize")
+    return out, float(scale.value)
 
 
 class PackedMLP:

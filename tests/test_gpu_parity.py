@@ -356,3 +356,54 @@ def test_full_size_llama7b_up_projection():
     ref = Xg.double() @ Wd
     assert float((Yg - ref).abs().max() / ref.abs().max()) <= TOL + 2.0 ** -11
     pw.check()
+
+
+def test_packed_weight_file_round_trip(tmp_path):
+    """tllm_weight_save / tllm_weight_load: the loaded handle reports the same layout and gives the same bits as
+    the one that was saved, on both kernels; a damaged file is refused with a message."""
+    rng = np.random.default_rng(31)
+    K, N = 3000, 1100
+    w = random_ternary(rng, K, N, 0.7)
+    pw = PackedWeight.from_dense(w, scale=0.0625)
+    path = tmp_path / "w.tllm"
+    pw.save(path)
+    pl = PackedWeight.load(path)
+    assert pl.info == pw.info
+    xs, X = int_acts(rng, 5, K, 16, torch.float32)
+    assert torch.equal(pl.matmul(X), pw.matmul(X))
+    assert np.array_equal(pl.matmul(X).double().cpu().numpy(), oracle.dense_f64(xs, w, 0.0625))
+    L = _lib.lib()
+    L.tllm_set_mma_min_rows(8)
+    xs, Xh = int_acts(rng, 40, K, 4, torch.float16)
+    Y = torch.empty((40, N), dtype=torch.float32, device=dev())
+    m0 = L.tllm_mma_launch_count()
+    pl.matmul(Xh, out=Y)
+    assert L.tllm_mma_launch_count() == m0 + 1
+    assert np.array_equal(Y.double().cpu().numpy(), oracle.dense_f64(xs, w, 0.0625))
+    L.tllm_set_mma_min_rows(0)
+    raw = path.read_bytes()
+    bad = tmp_path / "bad.tllm"
+    bad.write_bytes(raw[: len(raw) // 2])
+    with pytest.raises(RuntimeError, match="not a packed-weight file|truncated"):
+        PackedWeight.load(bad)
+    pw.close()
+    pl.close()
+
+
+def test_linear_from_float_weights():
+    """TernaryLinear.from_float: ternarise an nn.Linear weight (threshold rule), keep the per-tensor scale, and get
+    scale * x @ sign-pattern -- checked against the oracle's restatement of the rule and its dense product."""
+    g = torch.Generator().manual_seed(5)
+    lin = torch.nn.Linear(768, 320, bias=False)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(lin.weight.shape, generator=g) * 0.02)
+    tl = TernaryLinear.from_float(lin.weight, sparsity=0.6, bias=False, reference_buffers=False)
+    t_ref, s_ref = oracle.ternarize_f64(lin.weight.detach().t().contiguous().numpy(), sparsity=0.6)
+    assert np.array_equal(tl.ternary_weight.numpy(), t_ref.astype(np.int32)) and abs(tl.scale - s_ref) <= 1e-6 * s_ref
+    x = torch.randn((7, 768), generator=g)
+    y = tl(x.to(dev())).double().cpu().numpy()
+    ref = oracle.dense_f64(x.double().numpy(), t_ref, tl.scale)
+    assert rel_err(y, ref) <= TOL
+    # the ternarised layer approximates the float layer (sanity of the scale): correlation of the outputs is high
+    yf = (x @ lin.weight.t()).double().numpy()
+    assert np.corrcoef(y.ravel(), yf.ravel())[0, 1] > 0.8

@@ -170,3 +170,23 @@ def test_cpu_format_decoders_build_the_same_dense_matrix(cpu_reference):
     Wd = oracle.cpu_decode_dense(2, 8, 0, fx["grp.W.G8.min.i1.s0.meta"], fx["grp.W.G8.min.i1.s0.ri"], N, K)
     rc, out, _ = _roundtrip(Wd)
     assert rc == 0 and np.array_equal(out, fx["W"])
+
+
+@pytest.mark.parametrize("mode", [dict(sparsity=0.5), dict(sparsity=0.9), dict(threshold_factor=0.7), dict(threshold_factor=0.3)])
+def test_ternarize_matches_the_numpy_restatement(mode):
+    """tllm_ternarize on the host against oracle.ternarize_f64: identical ternary matrix, scale to fp32 rounding;
+    the requested sparsity is met exactly on data without ties."""
+    from ternaryllm_b200.weight import ternarize
+
+    rng = np.random.default_rng(21)
+    w = (rng.standard_normal((300, 130)) * 0.02).astype(np.float32)
+    t, s = ternarize(w, **mode)
+    tr, sr = oracle.ternarize_f64(w, **mode)
+    assert np.array_equal(t, tr)
+    assert abs(s - sr) <= 1e-6 * sr
+    assert set(np.unique(t)) <= {-1, 0, 1} and np.all(np.sign(w)[t != 0] == t[t != 0])
+    if "sparsity" in mode:
+        assert (t == 0).sum() == round(mode["sparsity"] * w.size)
+    # the scale minimises |w - s*t| over s for the chosen t
+    kept = t != 0
+    assert abs(s - np.abs(w[kept]).mean()) <= 1e-6 * s
