@@ -232,7 +232,7 @@ int tllm_silu_mul(void* g, const void* u, int dtype, int64_t n, void* stream);
 
 /* Glue between two products of a decoder layer, one launch: x[rows][hidden] += delta (skipped when delta is NULL),
  * then h = x * rsqrt(mean(x^2) + eps) * weight (weight = 1 when NULL); fp32 sums, all tensors of one float type,
- * device pointers.  The reference leaves the residual add and LlamaRMSNorm to stock Hugging Face modules
+ * device pointers aligned to 16 bytes, hidden a multiple of 8 (4 for fp32).  The reference leaves the residual add and LlamaRMSNorm to stock Hugging Face modules
  * (ternaryLLM_GPU/TernaryLLM/TernaryLlama.py); this entry point exists so that a decode step launches two
  * kernels per layer for them instead of a dozen element-wise ones. */
 int tllm_add_rmsnorm(void* x, const void* delta, const void* weight, void* h, int dtype, int rows, int hidden,

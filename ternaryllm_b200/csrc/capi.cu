@@ -891,8 +891,14 @@ int tllm_mlp_get_info(const tllm_mlp* m, tllm_weight_info* gate_up, tllm_weight_
 int tllm_add_rmsnorm(void* x, const void* delta, const void* weight, void* h, int dtype, int rows, int hidden, float eps, void* stream) {
     if (!x || !h || rows < 0 || hidden <= 0) return fail(TLLM_ERR_ARG, "tllm_add_rmsnorm: bad argument");
     if (dtype != TLLM_F32 && dtype != TLLM_F16 && dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "tllm_add_rmsnorm: unsupported dtype");
+    const int vec = dtype == TLLM_F32 ? 4 : 8;
+    if (hidden % vec || ((uintptr_t)x | (uintptr_t)h | (uintptr_t)delta | (uintptr_t)weight) % 16)
+        return fail(TLLM_ERR_ARG, "tllm_add_rmsnorm: hidden must be a multiple of %d and the pointers 16-byte aligned", vec);
     if (rows == 0) return TLLM_OK;
-    add_rmsnorm_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(x, delta, weight, h, dtype, hidden, eps);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == TLLM_F32) add_rmsnorm_kernel<float><<<(unsigned)rows, 256, 0, st>>>((float*)x, (const float*)delta, (const float*)weight, (float*)h, hidden, eps);
+    else if (dtype == TLLM_F16) add_rmsnorm_kernel<__half><<<(unsigned)rows, 256, 0, st>>>((__half*)x, (const __half*)delta, (const __half*)weight, (__half*)h, hidden, eps);
+    else add_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, st>>>((__nv_bfloat16*)x, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)weight, (__nv_bfloat16*)h, hidden, eps);
     CU_TRY(cudaGetLastError());
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return TLLM_OK;

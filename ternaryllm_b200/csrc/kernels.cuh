@@ -791,18 +791,92 @@ __global__ void silu_mul_kernel(void* g, const void* u, int dtype, long long n) 
 // Residual add and RMS normalisation of one row per block, the glue between two ternary products of a decoder
 // layer:  x[r] += delta[r] (when delta is given, rounded once to x's type);  h[r] = x[r] * rsqrt(mean(x[r]^2) + eps)
 // * weight (weight = 1 when absent).  Sums in fp32; x, delta, h and weight share one 16-bit or 32-bit float type.
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(void* x, const void* delta, const void* weight, void* h, int dtype, int hidden, float eps) {
+// A thread keeps up to four 16-byte vectors of its row in registers between the two passes (rows of up to
+// 8192 16-bit or 4096 32-bit values are read once); longer rows re-read the remainder.
+template <typename T>
+struct RmsVec;   // 16 bytes of T as floats
+template <>
+struct RmsVec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 a = __ldcg((const float4*)p);
+        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[8]) { *(float4*)p = make_float4(v[0], v[1], v[2], v[3]); }
+    static __device__ __forceinline__ float round(float v) { return v; }
+};
+template <>
+struct RmsVec<__half> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
+        const uint4 a = __ldcg((const uint4*)p);
+        const __half2* h = (const __half2*)&a;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x, v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__half* p, const float (&v)[8]) {
+        uint4 a;
+        __half2* h = (__half2*)&a;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        *(uint4*)p = a;
+    }
+    static __device__ __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+};
+template <>
+struct RmsVec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 a = __ldcg((const uint4*)p);
+        const __nv_bfloat162* h = (const __nv_bfloat162*)&a;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x, v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        uint4 a;
+        __nv_bfloat162* h = (__nv_bfloat162*)&a;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *(uint4*)p = a;
+    }
+    static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+// hidden must be a multiple of the vector width and all pointers 16-byte aligned (checked by the caller)
+template <typename T>
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(T* x, const T* delta, const T* weight, T* h, int hidden, float eps) {
+    constexpr int N = RmsVec<T>::N, KEEP = 4;
     __shared__ float red[8];
     const size_t row = (size_t)blockIdx.x * hidden;
+    const int nvec = hidden / N;
+    float keep[KEEP][8];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += 256) {
-        float v = load_act_f32_cg(x, dtype, row + i);
+    auto first_pass = [&](int vi, float (&v)[8]) {
+        RmsVec<T>::load(x + row + (size_t)vi * N, v);
         if (delta) {
-            v += load_act_f32_cg(delta, dtype, row + i);
-            v = dtype == TLLM_F32 ? v : dtype == TLLM_F16 ? __half2float(__float2half_rn(v)) : __bfloat162float(__float2bfloat16_rn(v));
-            store_out(x, dtype, row + i, v);
+            float d[8];
+            RmsVec<T>::load(delta + row + (size_t)vi * N, d);
+#pragma unroll
+            for (int i = 0; i < N; ++i) v[i] = RmsVec<T>::round(v[i] + d[i]);
+            RmsVec<T>::store(x + row + (size_t)vi * N, v);
         }
-        ss += v * v;
+#pragma unroll
+        for (int i = 0; i < N; ++i) ss += v[i] * v[i];
+    };
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+        const int vi = threadIdx.x + k * 256;
+        if (vi < nvec) first_pass(vi, keep[k]);
+    }
+    for (int vi = threadIdx.x + KEEP * 256; vi < nvec; vi += 256) {
+        float v[8];
+        first_pass(vi, v);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -812,10 +886,27 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(void* x, const void* d
 #pragma unroll
     for (int w = 0; w < 8; ++w) tot += red[w];
     const float inv = rsqrtf(tot / (float)hidden + eps);
-    for (int i = threadIdx.x; i < hidden; i += 256) {
-        const float v = load_act_f32_cg(x, dtype, row + i);
-        const float g = weight ? load_act_f32(weight, dtype, (size_t)i) : 1.f;
-        store_out(h, dtype, row + i, v * inv * g);
+    auto second_pass = [&](int vi, float (&v)[8]) {
+        if (weight) {
+            float g[8];
+            RmsVec<T>::load(weight + (size_t)vi * N, g);
+#pragma unroll
+            for (int i = 0; i < N; ++i) v[i] = v[i] * inv * g[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < N; ++i) v[i] = v[i] * inv;
+        }
+        RmsVec<T>::store(h + row + (size_t)vi * N, v);
+    };
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+        const int vi = threadIdx.x + k * 256;
+        if (vi < nvec) second_pass(vi, keep[k]);
+    }
+    for (int vi = threadIdx.x + KEEP * 256; vi < nvec; vi += 256) {
+        float v[8];
+        RmsVec<T>::load(x + row + (size_t)vi * N, v);     // written by this thread in the first pass, or untouched
+        second_pass(vi, v);
     }
 }
 

@@ -405,5 +405,5 @@ def test_linear_from_float_weights():
     ref = oracle.dense_f64(x.double().numpy(), t_ref, tl.scale)
     assert rel_err(y, ref) <= TOL
     # the ternarised layer approximates the float layer (sanity of the scale): correlation of the outputs is high
-    yf = (x @ lin.weight.t()).double().numpy()
+    yf = (x @ lin.weight.detach().t()).double().numpy()
     assert np.corrcoef(y.ravel(), yf.ravel())[0, 1] > 0.8
