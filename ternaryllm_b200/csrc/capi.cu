@@ -103,6 +103,7 @@ struct tllm_weight {
     void* d_x = nullptr;
     void* d_y = nullptr;
     void* h_pin = nullptr;
+    int* h_status = nullptr;        // pinned copy of the status word, read back with every host-buffer call
     size_t x_cap = 0, y_cap = 0, pin_cap = 0;
     cudaStream_t own_stream = nullptr;
     long long* d_trace = nullptr;   // diagnostics: see tllm_weight_set_trace
@@ -499,6 +500,7 @@ int tllm_weight_destroy(tllm_weight* w) {
     cudaFree(w->d_x);
     cudaFree(w->d_y);
     if (w->h_pin) cudaFreeHost(w->h_pin);
+    if (w->h_status) cudaFreeHost(w->h_status);
     if (w->own_stream) cudaStreamDestroy(w->own_stream);
     delete w;
     return TLLM_OK;
@@ -672,6 +674,7 @@ int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int
     const TsLayout& L = w->lay;
     const size_t xb = (size_t)rows * L.inners * dtype_size(x_dtype), yb = (size_t)rows * L.columns * dtype_size(y_dtype);
     if (!w->own_stream) CU_TRY(cudaStreamCreateWithFlags(&w->own_stream, cudaStreamNonBlocking));
+    if (!w->h_status) CU_TRY(cudaMallocHost((void**)&w->h_status, sizeof(int)));
     int r = ensure(&w->d_x, &w->x_cap, xb, false);
     if (r) return r;
     r = ensure(&w->d_y, &w->y_cap, yb, false);
@@ -681,11 +684,13 @@ int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int
     if (r) return r;
     if (y_layout == TLLM_ROW_MAJOR) {
         CU_TRY(cudaMemcpyAsync(Y, w->d_y, yb, cudaMemcpyDeviceToHost, w->own_stream));
+        CU_TRY(cudaMemcpyAsync(w->h_status, w->d_status, sizeof(int), cudaMemcpyDeviceToHost, w->own_stream));
         CU_TRY(cudaStreamSynchronize(w->own_stream));
     } else {
         r = ensure(&w->h_pin, &w->pin_cap, yb, true);
         if (r) return r;
         CU_TRY(cudaMemcpyAsync(w->h_pin, w->d_y, yb, cudaMemcpyDeviceToHost, w->own_stream));
+        CU_TRY(cudaMemcpyAsync(w->h_status, w->d_status, sizeof(int), cudaMemcpyDeviceToHost, w->own_stream));
         CU_TRY(cudaStreamSynchronize(w->own_stream));
         const size_t e = dtype_size(y_dtype);
         const char* src = (const char*)w->h_pin;
@@ -693,7 +698,8 @@ int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int
         for (int m = 0; m < rows; ++m)
             for (int n = 0; n < L.columns; ++n) std::memcpy(dst + ((size_t)n * rows + m) * e, src + ((size_t)m * L.columns + n) * e, e);
     }
-    return tllm_weight_check(w);
+    // the status word came back with the result; only a non-zero one needs the (synchronising) full check
+    return *w->h_status ? tllm_weight_check(w) : TLLM_OK;
 }
 
 }  // extern "C"
