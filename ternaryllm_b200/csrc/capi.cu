@@ -191,8 +191,9 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
 
 // true when the tensor-core kernel can take this call: fp16 / bf16 row-major activations whose rows TMA can address
 bool mm_usable(const tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, int rows) {
+    // (a TMA box is 64 values wide: narrower matrices stay on the gather kernel)
     if (!w->d_bits || (x_dtype != TLLM_F16 && x_dtype != TLLM_BF16) || x_layout != TLLM_ROW_MAJOR || ((uintptr_t)X % 16) || ((size_t)x_ld * 2 % 16) ||
-        tensor_map_encoder() == nullptr)
+        w->lay.inners < MM_TILE_K || tensor_map_encoder() == nullptr)
         return false;
     const int thr = mm_min_rows();
     if (thr == 0) return false;

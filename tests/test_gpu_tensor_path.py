@@ -146,6 +146,13 @@ def test_crossover_setting_and_fallbacks():
     pw.matmul(X.to(torch.float16)[:4].contiguous())
     assert mma_launches() == n0 + 1
     assert L.tllm_set_mma_min_rows(8) == 2
+    narrow = PackedWeight.from_dense(random_ternary(rng, 40, 256, 0.5))     # fewer rows of W than one TMA box: gather kernel
+    Xn = torch.tensor(rng.integers(-4, 5, size=(32, 40)).astype(np.float32), dtype=torch.float16, device=dev())
+    L.tllm_set_mma_min_rows(2)
+    narrow.matmul(Xn)
+    L.tllm_set_mma_min_rows(8)
+    assert mma_launches() == n0 + 1
+    narrow.close()
     lean = PackedWeight.from_dense(w, no_bit_tiles=1)       # no dense copy: always the gather kernel
     assert lean.info["bit_tile_bytes"] == 0
     Y = lean.matmul(X.to(torch.float16))
