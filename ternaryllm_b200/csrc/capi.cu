@@ -65,7 +65,7 @@ static int mm_min_rows() {
 // 9 us + 0.21 ps per matrix entry whatever the row count up to 64.  One row always takes the gather kernel.
 static bool mm_model_prefers_tensor(int64_t nnz, int64_t entries, int rows) {
     if (rows < 2) return false;
-    static const double g_ps[5] = {0.42, 0.55, 0.76, 1.38, 2.57};
+    static const double g_ps[5] = {0.42, 0.60, 0.85, 1.60, 3.00};   // ps per non-zero at 1, 2, 4, 8, 16 rows (between the 7B and 70B shapes)
     const int tail = rows % 16, full = rows / 16;
     int idx = 0;
     while ((1 << idx) < tail) ++idx;
