@@ -62,9 +62,11 @@ static int mm_min_rows() {
 }
 // Cost model measured on B200 (CUDA-graph replays, weights streamed from HBM): the gather kernel costs about
 // 6 us + nnz * g(rows padded to 1, 2, 4, 8, 16) per launch of at most 16 rows, the tensor-core kernel about
-// 9 us + 0.21 ps per matrix entry whatever the row count up to 64.  One row always takes the gather kernel.
+// 9 us + 0.21 ps per matrix entry whatever the row count up to 64.  One row always takes the gather kernel,
+// sixteen or more always the tensor-core kernel; the model decides in between.
 static bool mm_model_prefers_tensor(int64_t nnz, int64_t entries, int rows) {
     if (rows < 2) return false;
+    if (rows >= 16) return true;     // from 16 rows on the tensor-core kernel won on every shape and sparsity measured
     static const double g_ps[5] = {0.42, 0.60, 0.85, 1.60, 3.00};   // ps per non-zero at 1, 2, 4, 8, 16 rows (between the 7B and 70B shapes)
     const int tail = rows % 16, full = rows / 16;
     int idx = 0;
