@@ -31,26 +31,14 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+from ternaryllm_b200.synthetic import make_weight  # noqa: E402
+
 K_IN, N_OUT = 4096, 11008
 L2_BYTES = 126 * 1024 * 1024
 METRIC = "ternary_spmv_algorithmic_hbm_gbps"
 # DRAM bytes per launch of the decode kernel from an ncu capture of this workload at one row
 # (dram__bytes_read.sum + dram__bytes_write.sum = 23.70 MB + 0; profiles/tstream_spmm_decode_4096x11008_s75_m1.md).
 NCU_TRAFFIC_BYTES = 23.70e6
-
-
-def make_weight(seed: int, K: int, N: int, sparsity: float) -> np.ndarray:
-    """Seeded ternary matrix [K, N]: i.i.d. zeros with probability `sparsity` (rounded to a multiple of 1/256),
-    +1 and -1 equiprobable among the rest -- the reference's non-uniform generator (TernaryLinear.py:79-83) with a
-    byte-wide random source, which is what makes generating 10^8 entries take seconds."""
-    rng = np.random.default_rng(seed)
-    z = int(round(sparsity * 256))
-    half = (256 - z) // 2
-    r = rng.integers(0, 256, size=(K, N), dtype=np.uint8)
-    w = np.zeros((K, N), np.int8)
-    w[(r >= z) & (r < z + half)] = -1
-    w[r >= z + half] = 1
-    return w
 
 
 def algorithmic_bytes(nnz: int, K: int, N: int, M: int, e: int) -> int:
@@ -487,7 +475,7 @@ def main():
                    "algorithmic_bytes_per_launch": balg, "physical_bytes_per_launch": bphys, "nnz": nnz,
                    "us_per_launch": us_launch, "cuda_graph": graph is not None, "pdl": os.environ.get("TLLM_PDL", "1") != "0",
                    "accumulate": "fp32", "check_rel_err": err,
-                   "pack": {k: info[k] for k in ("tile_rows", "tiles", "col_blocks", "k_splits", "num_ctas", "lanes_per_list")}},
+                   "pack": {k: info[k] for k in ("tile_rows", "tiles", "col_blocks", "k_splits", "num_ctas", "units")}},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "frac_physical": (bphys / (us_launch * 1e-6) / 1e9) / peak, "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
                      "traffic": NCU_TRAFFIC_BYTES if (M == 1 and S == 0.75 and (K, N) == (K_IN, N_OUT)) else None},

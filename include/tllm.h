@@ -108,22 +108,24 @@ int tllm_ter_spmm(const void* X, int x_dtype, int x_layout, const int16_t* row_i
 typedef struct tllm_weight tllm_weight;
 
 typedef struct tllm_pack_opts {
-    int tile_rows;        /* rows of W covered by one shared-memory activation table; 0 = default (1024) */
+    int tile_rows;        /* rows of a K-tile: a multiple of 32, at most 4096; 0 = 4096 (one-byte ids cover 128 row groups
+                             of 32 rows; smaller tiles only make sense for tests of the multi-tile paths) */
     int num_ctas;         /* thread blocks to schedule for; 0 = number of SMs of the current device */
-    int lanes_per_list;   /* lanes that share one index list (power of two, 1..16); 0 = choose from density */
-    int max_rows;         /* largest M a single call may pass (scratch is sized for it); 0 = 16 */
-    int k_splits;         /* thread blocks that share one column block along K; 0 = choose (1 = no split-K scratch) */
+    int reserved0;        /* must be 0 */
+    int max_rows;         /* rows of one gather launch, 1..4 (the split-K scratch is sized for it); 0 = 4 */
+    int k_splits;         /* thread blocks that share one column range along K; 0 = choose (1 = no split-K scratch) */
     int no_bit_tiles;     /* 1 = do not keep the dense two-bit copy of W that the tensor-core kernel reads (every call
                              then runs the gather kernel); 0 = keep it (columns*inners/4 bytes) */
     int reserved[2];
 } tllm_pack_opts;
 
 typedef struct tllm_weight_info {
-    int inners, columns, tile_rows, tiles, col_blocks, k_splits, tiles_per_cta, num_ctas, lanes_per_list;
+    int inners, columns, tile_rows, tiles, col_blocks, k_splits, tiles_per_cta, num_ctas;
+    int units;                 /* (warp, K-tile, column range) work units of the index stream */
     int max_rows;
     int64_t nnz;               /* true non-zeros of W */
-    int64_t stream_bytes;      /* index stream as stored (with padding) */
-    int64_t meta_bytes;        /* list-offset metadata as stored */
+    int64_t stream_bytes;      /* index stream as stored: one byte per id, padding and list flags included */
+    int64_t meta_bytes;        /* block tables as stored */
     int64_t scratch_bytes;     /* split-K partial sums + counters owned by the handle */
     int64_t algorithmic_bytes; /* 2*nnz + 16*columns*ceil(inners/512): the reference layout's weight bytes */
     int64_t bit_tile_bytes;    /* dense two-bit copy read by the tensor-core kernel (0 if not kept) */
@@ -143,6 +145,12 @@ int tllm_weight_create_dense(const int8_t* w, int inners, int columns, float sca
 /* from the reference's merged tiled CSC arrays on the host (row ids as int32, as the packers return them) */
 int tllm_weight_create_mcsc(const int32_t* row_idx, const int32_t* col_off, int columns, int inners,
                             int tile_k, float scale, const tllm_pack_opts* opts, tllm_weight** out);
+/* from the reference's merged tiled CSC arrays as the reference's modules hold them: int16 row ids and the four int32
+ * per (column, tile), both in DEVICE memory (TernaryLinear.py:144-146).  Copies them to the host, checks every list
+ * offset against row_idx_len, decodes and repacks: the one-off step that lets code written against the reference's three
+ * buffers run the fast kernels (tllm_ter_spmm consumes the arrays as they are, one warp per column). */
+int tllm_weight_create_mcsc_device(const int16_t* row_idx, int64_t row_idx_len, const int32_t* col_off, int columns,
+                                   int inners, int tile_k, float scale, const tllm_pack_opts* opts, tllm_weight** out);
 /* from the reference's CPU formats (ternaryLLM_CPU/src/TCSC.hpp), host memory:
  *   kind 0 SparseFormat (:6-34): meta = col_start_neg[N+1] ++ col_start_pos[N+1], ri = neg ids ++ pos ids,
  *          aux = number of neg ids
@@ -155,17 +163,25 @@ int tllm_weight_create_cpu_format(int kind, int group, int chunk, const int32_t*
                                   int ri32, int64_t aux, int columns, int inners, float scale,
                                   const tllm_pack_opts* opts, tllm_weight** out);
 /* Diagnostic that needs no GPU: packs w for `num_sms` thread blocks on the host, checks the invariants the
- * kernel relies on (lists tile every block's range exactly, every work unit fits the ring, every ring stage
- * is handed back exactly once), unpacks into w_out (inners*columns int8) and fills info. */
+ * kernel relies on (every (tile, column) covered once, ids inside their tile, list counts, no lane more than a ring
+ * ahead of the reduced slots, reduce points only behind complete slots), unpacks into w_out (inners*columns int8)
+ * and fills info. */
 int tllm_pack_roundtrip(const int8_t* w, int inners, int columns, const tllm_pack_opts* opts, int num_sms,
                         int8_t* w_out, tllm_weight_info* info);
+/* Test hook that needs no GPU: packs w, overwrites one field of the packed image (what: 1 table word `where`, 2 stream
+ * byte `where`, 3 tile_rows, 4 tiles, 5 col_blocks, 6 k_splits, 7 tiles_per_cta, 8..9 / 12..13 a block descriptor's
+ * table words / first vector / table offset / vectors, 10 column range `where`, 11 inners; 0 = nothing) with `value` and
+ * runs the validator that tllm_weight_load runs before it uploads anything.  Returns its verdict. */
+int tllm_pack_corrupt_check(const int8_t* w, int inners, int columns, const tllm_pack_opts* opts, int num_sms,
+                            int what, int64_t where, uint32_t value);
 int tllm_weight_destroy(tllm_weight* w);
 int tllm_weight_get_info(const tllm_weight* w, tllm_weight_info* info);
-/* Packed-weight files: everything a handle holds on the device (index stream, section tables, block descriptors, the
+/* Packed-weight files: everything a handle holds on the device (index stream, block tables, block descriptors, the
  * dense two-bit copy if kept, the scale) in one file, so that a model is packed once and loaded without repacking.
  * The reference keeps its packed arrays as module buffers in a PyTorch state dict
  * (ternaryLLM_GPU/TernaryLLM/TernaryLinear.py:144-146); this is the equivalent for handles.  A file written on a
- * device with another SM count loads and runs (the gather kernel's block schedule is part of the file). */
+ * device with another SM count loads and runs (the gather kernel's block schedule is part of the file).  A file is
+ * validated in full on the host before anything is uploaded; a damaged or foreign file is refused with TLLM_ERR_ARG. */
 int tllm_weight_save(const tllm_weight* w, const char* path);
 int tllm_weight_load(const char* path, tllm_weight** out);
 /* change the per-tensor scale s (host value; takes effect for later calls) */
@@ -176,15 +192,10 @@ int tllm_weight_set_scale(tllm_weight* w, float scale);
  * and clears the condition. */
 int tllm_weight_check(tllm_weight* w);
 
-/* Diagnostics: while `device_buffer` (num_ctas*8 int64 in device memory) is set, every launch on this handle
- * records per thread block the GPU global timer (ns) at: 0 start, 1 ordered behind the previous kernel, 2 list
- * table arrived, 3 first activation table filled, 4 all lists consumed, 5 split-K arrival done, 6 end,
- * 7 last bulk copy issued.  NULL switches it off (the default). */
-int tllm_weight_set_trace(tllm_weight* w, void* device_buffer);
-
-/* Y[rows][columns] = X . W . s   on device pointers, launched on `stream`.  rows <= max_rows of the
- * handle per launch; larger row counts are processed in chunks.  Calls on one handle must not overlap
- * on the GPU (they share the handle's scratch); calls on different handles may. */
+/* Y[rows][columns] = X . W . s   on device pointers, launched on `stream`; the device that holds the handle must be
+ * current.  The gather kernel takes max_rows (at most four) rows per launch, larger row counts run as several
+ * launches or on the tensor-core kernel (tllm_set_mma_min_rows).  Calls on one handle must not overlap on the GPU
+ * (they share the handle's scratch); calls on different handles may. */
 int tllm_spmm(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y, int y_dtype,
               void* stream);
 
@@ -194,28 +205,35 @@ int tllm_spmm(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows
  * kernels' result layout (GEMM_CPU_FP32.cpp:534). */
 int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y, int y_dtype,
                    int y_layout);
+/* Same plus a bias: Y[m][n] = (X . W . s)[m][n] + bias[n], bias a host array of `columns` values of y_dtype (NULL = no
+ * bias).  The one place the reference adds a bias is sparseGEMM<T> (ternaryLLM_CPU/src/TCSC.hpp:413-430). */
+int tllm_spmm_host_bias(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, const void* bias,
+                        void* Y, int y_dtype, int y_layout);
 
 /* The same product for callers that are not allowed to allocate device memory -- a serving loop whose
  * memory budget was fixed at start-up, code living under a framework allocator it must not bypass, a path
  * where an allocation's implicit synchronisation is unacceptable.  (No counterpart in the reference: its
  * extension allocates its result on every call, ter_spmm_wrapper.cu:334.)  Inputs and outputs are the
- * caller's device buffers; the split-K partial sums, arrival counters and status word live in a fixed array
- * inside the library (about 4 MiB, held by every GPU that loads the library until the process exits) instead
- * of the scratch the handle got from cudaMalloc.  Nothing is allocated or freed here.
- *   Limit:  k_splits * min(rows, max_rows) * columns  <=  1 048 576 partial sums, and at most 256 column
- *           blocks; anything larger is refused with TLLM_ERR_ARG and a message (see tllm_weight_get_info).
+ * caller's device buffers; the split-K partial sums and arrival counters live in a fixed array inside the
+ * library (about 4 MiB, held by every GPU that loads the library until the process exits) instead of the
+ * scratch the handle got from cudaMalloc.  Nothing is allocated or freed here.  Always the gather kernel.
+ *   Limit:  k_splits * min(rows, max_rows) * columns  <=  1 048 576 partial sums (weights packed without a
+ *           K-split need none), and at most 4096 column blocks; anything larger is refused with TLLM_ERR_ARG
+ *           and a message (see tllm_weight_get_info).
  *   First call on a device looks up the array's device address (once per device, with that device current);
  *           make that first call outside any stream capture.
- *   All calls share the one array: the counters and status word are cleared in stream order at every call,
- *           but two calls that overlap on the GPU (different streams) race and give wrong results. */
+ *   All calls share the one array: the counters are cleared in stream order at every call, but two calls that
+ *           overlap on the GPU (different streams) race and give wrong results.
+ *   A kernel that gave up on a bounded wait reports through the handle's status word as on every other path:
+ *           tllm_weight_check(w). */
 int tllm_spmm_static_scratch(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y,
                              int y_dtype, void* stream);
 
 /* --------------------------------------------------------------------------------------------------
  * Fused ternary MLP block  y = down( silu(gate(x)) * up(x) )  (TernaryMLP.py:33-35;
  * TernaryMLP<T>::forward, ternaryLLM_CPU/src/LlamaModel.hpp:343-452): gate and up share one activation
- * table and one launch whose epilogue applies SiLU and the product; down follows as a dependent launch
- * whose weight stream is prefetched while the first kernel drains.
+ * table and one launch whose epilogue applies SiLU and the product; down follows as a second, dependent launch
+ * whose weight stream is prefetched while the first kernel drains (two launches per block, h through HBM).
  * -------------------------------------------------------------------------------------------------- */
 typedef struct tllm_mlp tllm_mlp;
 int tllm_mlp_create(const int8_t* w_gate, const int8_t* w_up, const int8_t* w_down, int hidden,
@@ -225,6 +243,10 @@ int tllm_mlp_destroy(tllm_mlp* m);
 /* X [rows][hidden] -> Y [rows][hidden]; H (device, rows*intermediate elements of x_dtype) receives the
  * intermediate activations and may be NULL to use the handle's own buffer. */
 int tllm_mlp_forward(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y, void* H, void* stream);
+/* Same with HOST buffers and the reference's in-place convention (TernaryMLP<T>::forward overwrites its input with the
+ * block's output, LlamaModel.hpp:343-452): X [rows][hidden] row-major is copied to the device, the block runs, the
+ * result is copied back over X; H (host, rows*intermediate values, may be NULL) receives silu(gate)*up. Synchronises. */
+int tllm_mlp_forward_host(tllm_mlp* m, void* X, int x_dtype, int rows, void* H);
 int tllm_mlp_get_info(const tllm_mlp* m, tllm_weight_info* gate_up, tllm_weight_info* down);
 
 /* Exact SiLU(x)*y epilogue on its own (Naive_SiLU_Dot, ternaryLLM_CPU/src/initData.hpp:204-210):

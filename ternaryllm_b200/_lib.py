@@ -17,13 +17,13 @@ ROW_MAJOR, COL_MAJOR = 0, 1
 
 
 class PackOpts(C.Structure):
-    _fields_ = [("tile_rows", C.c_int), ("num_ctas", C.c_int), ("lanes_per_list", C.c_int), ("max_rows", C.c_int),
+    _fields_ = [("tile_rows", C.c_int), ("num_ctas", C.c_int), ("reserved0", C.c_int), ("max_rows", C.c_int),
                 ("k_splits", C.c_int), ("no_bit_tiles", C.c_int), ("reserved", C.c_int * 2)]
 
 
 class WeightInfo(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("inners", "columns", "tile_rows", "tiles", "col_blocks", "k_splits",
-                                       "tiles_per_cta", "num_ctas", "lanes_per_list", "max_rows")] + [
+                                       "tiles_per_cta", "num_ctas", "units", "max_rows")] + [
         (n, C.c_int64) for n in ("nnz", "stream_bytes", "meta_bytes", "scratch_bytes", "algorithmic_bytes", "bit_tile_bytes")] + [
         ("scale", C.c_float)]
 
@@ -50,19 +50,22 @@ SIGNATURES = {
     "tllm_weight_load": (_I, [C.c_char_p, _P]),
     "tllm_weight_create_dense": (_I, [_P, _I, _I, _F, _P, _P]),
     "tllm_weight_create_mcsc": (_I, [_P, _P, _I, _I, _I, _F, _P, _P]),
+    "tllm_weight_create_mcsc_device": (_I, [_P, _L, _P, _I, _I, _I, _F, _P, _P]),
     "tllm_weight_create_cpu_format": (_I, [_I, _I, _I, _P, _P, _I, _L, _I, _I, _F, _P, _P]),
     "tllm_pack_roundtrip": (_I, [_P, _I, _I, _P, _I, _P, _P]),
+    "tllm_pack_corrupt_check": (_I, [_P, _I, _I, _P, _I, _I, _L, C.c_uint32]),
     "tllm_weight_destroy": (_I, [_P]),
     "tllm_weight_get_info": (_I, [_P, _P]),
     "tllm_weight_set_scale": (_I, [_P, _F]),
     "tllm_weight_check": (_I, [_P]),
-    "tllm_weight_set_trace": (_I, [_P, _P]),
     "tllm_spmm": (_I, [_P, _P, _I, _I, _I, _P, _I, _P]),
     "tllm_spmm_host": (_I, [_P, _P, _I, _I, _I, _P, _I, _I]),
+    "tllm_spmm_host_bias": (_I, [_P, _P, _I, _I, _I, _P, _P, _I, _I]),
     "tllm_spmm_static_scratch": (_I, [_P, _P, _I, _I, _I, _P, _I, _P]),
     "tllm_mlp_create": (_I, [_P, _P, _P, _I, _I, _F, _F, _F, _P, _P]),
     "tllm_mlp_destroy": (_I, [_P]),
     "tllm_mlp_forward": (_I, [_P, _P, _I, _I, _P, _P, _P]),
+    "tllm_mlp_forward_host": (_I, [_P, _P, _I, _I, _P]),
     "tllm_mlp_get_info": (_I, [_P, _P, _P]),
     "tllm_silu_mul": (_I, [_P, _P, _I, _L, _P]),
     "tllm_add_rmsnorm": (_I, [_P, _P, _P, _P, _I, _I, _I, _F, _P]),

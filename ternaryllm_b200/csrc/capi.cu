@@ -10,6 +10,7 @@
 
 #include <cudaTypedefs.h>
 
+#include "bstream_kernel.cuh"
 #include "kernels.cuh"
 #include "mma_kernel.cuh"
 #include "util.h"
@@ -44,8 +45,6 @@ static size_t dtype_size(int dt) {
     return 0;
 }
 
-// Activation rows from which the tensor-core kernel takes over from the gather kernel (measured crossover on
-// B200; TLLM_MMA_MIN_ROWS overrides it, 0 switches the tensor-core kernel off).
 // Which kernel takes a call: -1 = decide per call from a cost model of the two kernels (the default), 0 = never the
 // tensor-core kernel, n > 0 = from n activation rows on.  TLLM_MMA_MIN_ROWS sets the initial value.
 static std::atomic<int> g_mm_min_rows{-2};
@@ -60,29 +59,19 @@ static int mm_min_rows() {
     }
     return v;
 }
-// Cost model measured on B200 (CUDA-graph replays, weights streamed from HBM): the gather kernel costs about
-// 6 us + nnz * g(rows padded to 1, 2, 4, 8, 16) per launch of at most 16 rows, the tensor-core kernel about
-// 9 us + 0.21 ps per matrix entry whatever the row count up to 64.  One row always takes the gather kernel,
-// sixteen or more always the tensor-core kernel; the model decides in between.
+// Cost model measured on B200 (CUDA-graph replays, weights streamed from HBM), microseconds: a gather launch of up
+// to four rows costs about GATHER_FIXED + nnz * g(rows padded to 1, 2, 4), more rows take ceil(rows / 4) launches;
+// the tensor-core kernel about 9 + 0.21e-6 per matrix entry whatever the row count up to 64.  One row always takes
+// the gather kernel; the model decides from two rows on.
+static const double GATHER_FIXED_US = 3.0;
+static const double GATHER_PS_PER_NNZ[3] = {0.25, 0.40, 0.75};
 static bool mm_model_prefers_tensor(int64_t nnz, int64_t entries, int rows) {
     if (rows < 2) return false;
-    if (rows >= 16) return true;     // from 16 rows on the tensor-core kernel won on every shape and sparsity measured
-    static const double g_ps[5] = {0.42, 0.60, 0.85, 1.60, 3.00};   // ps per non-zero at 1, 2, 4, 8, 16 rows (between the 7B and 70B shapes)
-    const int tail = rows % 16, full = rows / 16;
-    int idx = 0;
-    while ((1 << idx) < tail) ++idx;
-    const double t_gather = full * (6.0 + nnz * g_ps[4] * 1e-6) + (tail ? 6.0 + nnz * g_ps[idx] * 1e-6 : 0.0);
+    const int full = rows / 4, tail = rows % 4;
+    const int idx = tail <= 1 ? 0 : (tail == 2 ? 1 : 2);
+    const double t_gather = full * (GATHER_FIXED_US + nnz * GATHER_PS_PER_NNZ[2] * 1e-6) + (tail ? GATHER_FIXED_US + nnz * GATHER_PS_PER_NNZ[idx] * 1e-6 : 0.0);
     const double t_tensor = 9.0 + entries * 0.21e-6 * (rows <= 64 ? 1.0 : rows / 64.0);
     return t_tensor < t_gather;
-}
-
-static bool pdl_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("TLLM_PDL");
-        v = (e && e[0] == '0') ? 0 : 1;
-    }
-    return v == 1;
 }
 
 }  // namespace tllm
@@ -90,10 +79,11 @@ static bool pdl_enabled() {
 using namespace tllm;
 
 struct tllm_weight {
-    TsLayout lay;
+    BsLayout lay;
     float scale = 1.f;
     int device = 0;
-    int max_rows = 16;
+    int max_rows = 4;                 // rows of one gather launch
+    uint32_t max_meta_words = 0;      // longest block table
     uint4* d_stream = nullptr;
     uint32_t* d_meta = nullptr;
     TsCtaDesc* d_cta = nullptr;
@@ -101,20 +91,24 @@ struct tllm_weight {
     unsigned int* d_counters = nullptr;
     int* d_status = nullptr;
     size_t stream_bytes = 0, meta_bytes = 0, scratch_bytes = 0;
-    // staging for the host-buffer entry point
+    // staging for the host-buffer entry points
     void* d_x = nullptr;
     void* d_y = nullptr;
+    void* d_bias = nullptr;
     void* h_pin = nullptr;
     int* h_status = nullptr;        // pinned copy of the status word, read back with every host-buffer call
-    size_t x_cap = 0, y_cap = 0, pin_cap = 0;
+    size_t x_cap = 0, y_cap = 0, bias_cap = 0, pin_cap = 0;
     cudaStream_t own_stream = nullptr;
-    long long* d_trace = nullptr;   // diagnostics: see tllm_weight_set_trace
     // tensor-core kernel: dense two-bit copy of W and its split scratch
     uint4* d_bits = nullptr;
     float* d_mm_partial = nullptr;
     unsigned int* d_mm_counters = nullptr;
     size_t bits_bytes = 0;
     int mm_n_tiles = 0, mm_kb = 0, mm_grid = 0;
+    // the activation tensor map of the last tensor-core launch (encoding one costs more than a short launch)
+    CUtensorMap tmap;
+    const void* tmap_x = nullptr;
+    int tmap_dtype = -1, tmap_rows = 0, tmap_ld = 0, tmap_nt = 0;
 };
 
 struct tllm_mlp {
@@ -124,13 +118,23 @@ struct tllm_mlp {
     float s_gate = 1.f, s_up = 1.f;
     void* d_h = nullptr;
     size_t h_cap = 0;
+    // staging for the host-buffer entry point
+    void* d_x = nullptr;
+    void* d_y = nullptr;
+    size_t x_cap = 0, y_cap = 0;
 };
 
 namespace {
 
-template <typename ACC, int MP, int NW, int D, int NB>
-int launch_ts(const TsParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = tstream_spmm_kernel<ACC, MP, NW, D, NB>;
+// scratch of one gather launch: the handle's own, or the library's built-in array (tllm_spmm_static_scratch)
+struct Scratch {
+    void* partial;
+    unsigned int* counters;
+};
+
+template <typename ACC, int MP>
+int launch_bs(const BsParams& p, int grid, size_t smem, cudaStream_t st) {
+    auto kern = bstream_spmm_kernel<ACC, MP, 4, 3>;
     static std::mutex mu;
     static bool configured[64] = {};
     int dev = 0;
@@ -138,34 +142,23 @@ int launch_ts(const TsParams& p, int grid, size_t smem, cudaStream_t st) {
     {
         std::lock_guard<std::mutex> lk(mu);
         if (dev < 64 && !configured[dev]) {
-            CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
             configured[dev] = true;
         }
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(NW * 32);
+    cfg.blockDim = dim3(BS_WARPS * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = 1;
     CU_TRY(cudaLaunchKernelEx(&cfg, kern, p));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return TLLM_OK;
-}
-
-template <typename ACC>
-int dispatch_ts(const TsParams& p, int grid, size_t smem, cudaStream_t st) {
-    // rows are padded to 1, 2, 4, 8 or 16; up to four rows run 24 warps with two batches of four index vectors
-    // per lane, wider tiles trade warps and batch size for registers
-    if (p.M <= 1) return launch_ts<ACC, 1, 24, 4, 2>(p, grid, smem, st);
-    if (p.M <= 2) return launch_ts<ACC, 2, 24, 4, 2>(p, grid, smem, st);
-    if (p.M <= 4) return launch_ts<ACC, 4, 24, 4, 2>(p, grid, smem, st);
-    if (p.M <= 8) return launch_ts<ACC, 8, 16, 2, 2>(p, grid, smem, st);
-    return launch_ts<ACC, 16, 16, 2, 2>(p, grid, smem, st);
 }
 
 int check_types(int x_dtype, int y_dtype, const char* who) {
@@ -175,6 +168,15 @@ int check_types(int x_dtype, int y_dtype, const char* who) {
     }
     if (x_dtype != TLLM_F32 && x_dtype != TLLM_F16 && x_dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "%s: unsupported x_dtype %d", who, x_dtype);
     if (y_dtype != TLLM_F32 && y_dtype != TLLM_F16 && y_dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "%s: unsupported y_dtype %d", who, y_dtype);
+    return TLLM_OK;
+}
+
+// The handle's buffers live on one device; a call made with another device current would launch there with
+// pointers from two GPUs.
+int check_device(const tllm_weight* w, const char* who) {
+    int dev = 0;
+    CU_TRY(cudaGetDevice(&dev));
+    if (dev != w->device) return fail(TLLM_ERR_ARG, "%s: the weight lives on device %d but device %d is current", who, w->device, dev);
     return TLLM_OK;
 }
 
@@ -206,7 +208,7 @@ bool mm_usable(const tllm_weight* w, const void* X, int x_dtype, int x_layout, i
 // the whole product of `rows` activation rows in one launch of the tensor-core kernel
 int run_mm(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void* Y, int y_dtype, int y_ld, int epilogue, float scale,
            float scale2, cudaStream_t st) {
-    const TsLayout& L = w->lay;
+    const BsLayout& L = w->lay;
     MmParams p{};
     p.bits = w->d_bits;
     p.Y = Y;
@@ -228,12 +230,6 @@ int run_mm(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void*
     p.UK = p.Nt <= 64 ? 4 : 2;
     p.S = p.Nt == 128 ? 3 : 2;
     p.R = p.Nt == 64 ? 4 : 8;
-    // (environment overrides for tuning runs: TLLM_MM_UK, TLLM_MM_S, TLLM_MM_R)
-    if (const char* e = getenv("TLLM_MM_UK")) p.UK = atoi(e);
-    if (const char* e = getenv("TLLM_MM_S")) p.S = atoi(e);
-    if (const char* e = getenv("TLLM_MM_R")) p.R = atoi(e);
-    if ((p.UK != 1 && p.UK != 2 && p.UK != 4) || p.S < 1 || p.S > MM_MAX_STAGES || p.R < 1 || p.R > MM_MAX_RAW)
-        return fail(TLLM_ERR_ARG, "tensor-core kernel: bad ring configuration");
     p.KBU = (p.KB + p.UK - 1) / p.UK;
     p.split = p.Nt <= MM_SPLIT_MAX_NT ? 1 : 0;
     const uint32_t fmt = x_dtype == TLLM_BF16 ? 1u : 0u;
@@ -247,24 +243,29 @@ int run_mm(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void*
     p.scale = fmt ? scale * 0.5f : scale;
     p.scale2 = fmt ? scale2 * 0.5f : scale2;
 
-    CUtensorMap tmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)L.inners, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)x_ld * 2u};
-    const cuuint32_t box[2] = {MM_TILE_K, (cuuint32_t)p.Nt};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult cr = tensor_map_encoder()(&tmap, fmt ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(X), dims,
-                                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (cr != CUDA_SUCCESS) return fail(TLLM_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
+    if (w->tmap_x != X || w->tmap_dtype != x_dtype || w->tmap_rows != rows || w->tmap_ld != x_ld || w->tmap_nt != p.Nt) {
+        const cuuint64_t dims[2] = {(cuuint64_t)L.inners, (cuuint64_t)rows};
+        const cuuint64_t strides[1] = {(cuuint64_t)x_ld * 2u};
+        const cuuint32_t box[2] = {MM_TILE_K, (cuuint32_t)p.Nt};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult cr = tensor_map_encoder()(&w->tmap, fmt ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(X), dims,
+                                                 strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) {
+            w->tmap_x = nullptr;
+            return fail(TLLM_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
+        }
+        w->tmap_x = X, w->tmap_dtype = x_dtype, w->tmap_rows = rows, w->tmap_ld = x_ld, w->tmap_nt = p.Nt;
+    }
 
     const size_t smem = 1024 + (size_t)p.S * p.UK * (MM_A_STAGE_BYTES + (size_t)p.Nt * 128) + (size_t)p.R * p.UK * MM_CHUNK_BYTES + 512;
     if (smem > 227 * 1024) return fail(TLLM_ERR_ARG, "tensor-core kernel: ring configuration needs %zu bytes of shared memory", smem);
-    void (*kern)(CUtensorMap, MmParams) = p.UK == 4 ? mma_spmm_kernel<4> : p.UK == 2 ? mma_spmm_kernel<2> : mma_spmm_kernel<1>;
+    void (*kern)(CUtensorMap, MmParams) = p.UK == 4 ? mma_spmm_kernel<4> : mma_spmm_kernel<2>;
     static std::mutex mu;
-    static bool configured[64][3] = {};
+    static bool configured[64][2] = {};
     {
         std::lock_guard<std::mutex> lk(mu);
-        const int slot = p.UK == 4 ? 2 : p.UK == 2 ? 1 : 0;
+        const int slot = p.UK == 4 ? 1 : 0;
         if (w->device < 64 && !configured[w->device][slot]) {
             CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
             configured[w->device][slot] = true;
@@ -282,24 +283,31 @@ int run_mm(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void*
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    CU_TRY(cudaLaunchKernelEx(&cfg, kern, tmap, p));
+    cfg.numAttrs = 1;
+    CU_TRY(cudaLaunchKernelEx(&cfg, kern, w->tmap, p));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     g_mm_launches.fetch_add(1, std::memory_order_relaxed);
     return TLLM_OK;
 }
 
-// one launch of at most max_rows rows
-int run_ts(tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, int rows, void* Y, int y_dtype, int y_ld,
-           int epilogue, float scale, float scale2, cudaStream_t st) {
-    const TsLayout& L = w->lay;
-    TsParams p{};
+// K-tiles whose activation tables one launch keeps in shared memory: 64.5 KiB of tables at most
+int resident_tiles(int mp, int tiles_per_cta) {
+    const int fit = 4 / mp;
+    return tiles_per_cta < fit ? tiles_per_cta : fit;
+}
+
+// one gather launch of at most four rows
+int run_bs(tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, int rows, void* Y, int y_dtype, int y_ld,
+           int epilogue, float scale, float scale2, const Scratch& scr, cudaStream_t st) {
+    const BsLayout& L = w->lay;
+    const int mp = rows <= 1 ? 1 : (rows == 2 ? 2 : 4);
+    BsParams p{};
     p.stream = w->d_stream;
     p.meta = w->d_meta;
     p.X = X;
     p.Y = Y;
-    p.partial = w->d_partial;
-    p.counters = w->d_counters;
+    p.partial = scr.partial;
+    p.counters = scr.counters;
     p.status = w->d_status;
     p.x_dtype = x_dtype;
     p.x_layout = x_layout;
@@ -308,38 +316,56 @@ int run_ts(tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, i
     p.K = L.inners;
     p.N = L.columns;
     p.T = L.tile_rows;
-    p.tiles = L.tiles;
     p.col_blocks = L.col_blocks;
-    p.cols_per_block = L.cols_per_block;
-    p.sub_cols = L.sub_cols;
     p.k_splits = L.k_splits;
     p.tiles_per_cta = L.tiles_per_cta;
-    int lg = 0;
-    while ((1 << lg) < L.lanes_per_list) ++lg;
-    p.lpl_log2 = lg;
+    p.max_cols = L.max_cols_per_block;
+    p.resident = resident_tiles(mp, L.tiles_per_cta);
     p.epilogue = epilogue;
     p.y_ld = y_ld;
     p.x_ld = x_ld;
+    const size_t e = dtype_size(x_dtype);
+    p.x_vec = x_layout == TLLM_ROW_MAJOR && ((uintptr_t)X % 16 == 0) && ((size_t)x_ld * e % 16 == 0) && (L.inners % 16 == 0) && (L.tile_rows % 16 == 0);
+    p.l2_prefetch_bytes = 256u * 1024u;
     p.scale = scale;
     p.scale2 = scale2;
-    p.trace = w->d_trace;
-    p.l2_mode = 1;
+    const BsSmem sm = bs_smem_layout(mp, p.resident, L.tiles_per_cta, L.max_cols_per_block, w->max_meta_words);
+    p.off_table = sm.off_table, p.off_cells = sm.off_cells, p.off_meta = sm.off_meta, p.off_bars = sm.off_bars;
+    if (sm.total > 227u * 1024u) return fail(TLLM_ERR_ARG, "gather kernel: this weight needs %u bytes of shared memory per block", sm.total);
     p.cta_ext = w->d_cta;
-    std::memcpy(p.cta, L.cta.data(), sizeof(TsCtaDesc) * (size_t)(L.num_ctas < TS_MAX_CTAS ? L.num_ctas : TS_MAX_CTAS));
-    // bulk-copy staging of the activation tile needs every row segment to start and end on 16 bytes
-    const size_t e = dtype_size(x_dtype);
-    p.x_tma = x_layout == TLLM_ROW_MAJOR && ((uintptr_t)X % 16 == 0) && ((size_t)x_ld * e % 16 == 0) && ((size_t)L.tile_rows * e % 16 == 0) &&
-              ((size_t)L.inners * e % 16 == 0);
-    if (x_dtype == TLLM_I8) return dispatch_ts<int>(p, L.num_ctas, TS_SMEM_TOTAL, st);
-    return dispatch_ts<float>(p, L.num_ctas, TS_SMEM_TOTAL, st);
+    std::memcpy(p.cta, L.cta.data(), sizeof(TsCtaDesc) * (size_t)(L.num_ctas < BS_MAX_PARAM_BLOCKS ? L.num_ctas : BS_MAX_PARAM_BLOCKS));
+    if (x_dtype == TLLM_I8) {
+        if (mp == 1) return launch_bs<int, 1>(p, L.num_ctas, sm.total, st);
+        if (mp == 2) return launch_bs<int, 2>(p, L.num_ctas, sm.total, st);
+        return launch_bs<int, 4>(p, L.num_ctas, sm.total, st);
+    }
+    if (mp == 1) return launch_bs<float, 1>(p, L.num_ctas, sm.total, st);
+    if (mp == 2) return launch_bs<float, 2>(p, L.num_ctas, sm.total, st);
+    return launch_bs<float, 4>(p, L.num_ctas, sm.total, st);
 }
 
-int upload(tllm_weight* w, const TsHostImage& img, float scale, int max_rows) {
+// the gather product of any number of rows: launches of up to max_rows rows
+int run_gather(tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, int rows, void* Y, int y_dtype, int y_ld, int epilogue,
+               float scale, float scale2, const Scratch& scr, cudaStream_t st) {
+    const size_t xe = dtype_size(x_dtype), ye = dtype_size(y_dtype);
+    for (int r0 = 0; r0 < rows; r0 += w->max_rows) {
+        const int m = rows - r0 < w->max_rows ? rows - r0 : w->max_rows;
+        const char* xp = (const char*)X + (x_layout == TLLM_ROW_MAJOR ? (size_t)r0 * x_ld : (size_t)r0) * xe;
+        char* yp = (char*)Y + (size_t)r0 * y_ld * ye;
+        const int r = run_bs(w, xp, x_dtype, x_layout, x_ld, m, yp, y_dtype, y_ld, epilogue, scale, scale2, scr, st);
+        if (r) return r;
+    }
+    return TLLM_OK;
+}
+
+int upload(tllm_weight* w, const BsHostImage& img, float scale, int max_rows) {
     w->lay = img.lay;
     w->scale = scale;
     w->max_rows = max_rows;
+    w->max_meta_words = 0;
+    for (const TsCtaDesc& d : img.lay.cta) w->max_meta_words = d.meta_words > w->max_meta_words ? d.meta_words : w->max_meta_words;
     CU_TRY(cudaGetDevice(&w->device));
-    w->stream_bytes = img.stream.size() * sizeof(uint16_t);
+    w->stream_bytes = img.stream.size();
     w->meta_bytes = img.meta.size() * sizeof(uint32_t);
     CU_TRY(cudaMalloc(&w->d_stream, w->stream_bytes + 512));
     CU_TRY(cudaMalloc(&w->d_meta, w->meta_bytes + 16));
@@ -347,7 +373,7 @@ int upload(tllm_weight* w, const TsHostImage& img, float scale, int max_rows) {
     CU_TRY(cudaMemcpy(w->d_meta, img.meta.data(), w->meta_bytes, cudaMemcpyHostToDevice));
     CU_TRY(cudaMalloc(&w->d_cta, img.lay.cta.size() * sizeof(TsCtaDesc)));
     CU_TRY(cudaMemcpy(w->d_cta, img.lay.cta.data(), img.lay.cta.size() * sizeof(TsCtaDesc), cudaMemcpyHostToDevice));
-    const size_t partial_bytes = (size_t)img.lay.k_splits * max_rows * img.lay.columns * 4;
+    const size_t partial_bytes = img.lay.k_splits > 1 ? (size_t)img.lay.k_splits * max_rows * img.lay.columns * 4 : 16;
     const size_t counter_bytes = (size_t)img.lay.col_blocks * sizeof(unsigned int);
     w->scratch_bytes = partial_bytes + counter_bytes + sizeof(int);
     CU_TRY(cudaMalloc(&w->d_partial, partial_bytes));
@@ -357,14 +383,6 @@ int upload(tllm_weight* w, const TsHostImage& img, float scale, int max_rows) {
     CU_TRY(cudaMemset(w->d_status, 0, sizeof(int)));
     CU_TRY(cudaDeviceSynchronize());
     return TLLM_OK;
-}
-
-int upload_bit_tiles(tllm_weight* w, const std::vector<uint32_t>& bits, int sms);
-
-int upload_bits(tllm_weight* w, const int8_t* dense, int inners, int columns, int sms) {
-    std::vector<uint32_t> bits;
-    mm_pack_bits(dense, inners, columns, &bits, &w->mm_n_tiles, &w->mm_kb);
-    return upload_bit_tiles(w, bits, sms);
 }
 
 int upload_bit_tiles(tllm_weight* w, const std::vector<uint32_t>& bits, int sms) {
@@ -382,24 +400,36 @@ int upload_bit_tiles(tllm_weight* w, const std::vector<uint32_t>& bits, int sms)
     return TLLM_OK;
 }
 
+int upload_bits(tllm_weight* w, const int8_t* dense, int inners, int columns, int sms) {
+    std::vector<uint32_t> bits;
+    mm_pack_bits(dense, inners, columns, &bits, &w->mm_n_tiles, &w->mm_kb);
+    return upload_bit_tiles(w, bits, sms);
+}
+
+int device_sms(int* sms) {
+    int dev = 0;
+    CU_TRY(cudaGetDevice(&dev));
+    CU_TRY(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev));
+    int max_smem = 0;
+    CU_TRY(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    if (max_smem < 227 * 1024)
+        return fail(TLLM_ERR_ARG, "this device offers %d bytes of shared memory per block; the kernels need 232448 (built for sm_100a)", max_smem);
+    return TLLM_OK;
+}
+
 int create_from_dense(const int8_t* dense, int inners, int columns, float scale, const tllm_pack_opts* opts, tllm_weight** out) {
     if (!out) return fail(TLLM_ERR_ARG, "weight create: out is NULL");
     *out = nullptr;
-    int dev = 0, sms = 0;
-    CU_TRY(cudaGetDevice(&dev));
-    CU_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    int max_smem = 0;
-    CU_TRY(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    if ((int)TS_SMEM_TOTAL > max_smem)
-        return fail(TLLM_ERR_ARG, "this device offers %d bytes of shared memory per block; the kernel needs %u (built for sm_100a)", max_smem, (unsigned)TS_SMEM_TOTAL);
-    TsHostImage img;
-    if (sms > TS_MAX_CTAS) sms = TS_MAX_CTAS;
-    const char* msg = ts_pack_dense(dense, inners, columns, opts, sms, &img);
+    int sms = 0;
+    int rc = device_sms(&sms);
+    if (rc) return rc;
+    BsHostImage img;
+    const char* msg = bs_pack_dense(dense, inners, columns, opts, sms, &img);
     if (msg) return fail(TLLM_ERR_ARG, "%s", msg);
-    int max_rows = (opts && opts->max_rows > 0) ? opts->max_rows : 16;
-    if (max_rows > 16) max_rows = 16;
+    int max_rows = (opts && opts->max_rows > 0) ? opts->max_rows : 4;
+    if (max_rows > 4) max_rows = 4;
     tllm_weight* w = new tllm_weight();
-    int rc = upload(w, img, scale, max_rows);
+    rc = upload(w, img, scale, max_rows);
     if (rc == TLLM_OK && !(opts && opts->no_bit_tiles)) rc = upload_bits(w, dense, inners, columns, sms);
     if (rc != TLLM_OK) {
         tllm_weight_destroy(w);
@@ -424,12 +454,37 @@ int ensure(void** p, size_t* cap, size_t need, bool pinned) {
     return TLLM_OK;
 }
 
+// Y[rows][columns] (row-major, on the device) += bias[columns], both of y_dtype
+int add_bias(void* Y, const void* bias, int y_dtype, int rows, int columns, cudaStream_t st) {
+    const long long n = (long long)rows * columns;
+    bias_add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(Y, bias, y_dtype, n, columns);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return TLLM_OK;
+}
+
 }  // namespace
+
+namespace tllm {
+void bs_fill_info(const BsLayout& L, tllm_weight_info* info) {
+    info->inners = L.inners;
+    info->columns = L.columns;
+    info->tile_rows = L.tile_rows;
+    info->tiles = L.tiles;
+    info->col_blocks = L.col_blocks;
+    info->k_splits = L.k_splits;
+    info->tiles_per_cta = L.tiles_per_cta;
+    info->num_ctas = L.num_ctas;
+    info->units = (int)L.units;
+    info->nnz = L.nnz;
+    info->algorithmic_bytes = 2 * L.nnz + 16 * (int64_t)L.columns * ((L.inners + 511) / 512);
+}
+}  // namespace tllm
 
 extern "C" {
 
 const char* tllm_last_error(void) { return g_err.c_str(); }
-int tllm_version(void) { return 100; }
+int tllm_version(void) { return 200; }
 int64_t tllm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 int64_t tllm_mma_launch_count(void) { return g_mm_launches.load(std::memory_order_relaxed); }
 int tllm_set_mma_min_rows(int rows) {
@@ -480,6 +535,22 @@ int tllm_weight_create_mcsc(const int32_t* row_idx, const int32_t* col_off, int 
     return create_from_dense(dense.data(), inners, columns, scale, opts, out);
 }
 
+int tllm_weight_create_mcsc_device(const int16_t* row_idx, int64_t row_idx_len, const int32_t* col_off, int columns, int inners, int tile_k,
+                                   float scale, const tllm_pack_opts* opts, tllm_weight** out) {
+    if (!row_idx || !col_off || columns <= 0 || inners <= 0 || tile_k <= 0 || row_idx_len < 0)
+        return fail(TLLM_ERR_ARG, "tllm_weight_create_mcsc_device: bad argument");
+    const size_t n_off = (size_t)columns * ((size_t)(inners + tile_k - 1) / tile_k) * 4;
+    std::vector<int16_t> ri16((size_t)row_idx_len);
+    std::vector<int32_t> off(n_off);
+    if (row_idx_len) CU_TRY(cudaMemcpy(ri16.data(), row_idx, ri16.size() * sizeof(int16_t), cudaMemcpyDeviceToHost));
+    CU_TRY(cudaMemcpy(off.data(), col_off, off.size() * sizeof(int32_t), cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < n_off; i += 4)
+        if (off[i] < 0 || off[i + 1] < off[i] || off[i + 2] < off[i + 1] || off[i + 2] > row_idx_len)
+            return fail(TLLM_ERR_ARG, "tllm_weight_create_mcsc_device: list offsets of entry %zu leave the row-index array", i / 4);
+    std::vector<int32_t> ri(ri16.begin(), ri16.end());
+    return tllm_weight_create_mcsc(ri.data(), off.data(), columns, inners, tile_k, scale, opts, out);
+}
+
 int tllm_weight_create_cpu_format(int kind, int group, int chunk, const int32_t* meta, const void* ri, int ri32, int64_t aux,
                                   int columns, int inners, float scale, const tllm_pack_opts* opts, tllm_weight** out) {
     if (!meta || !ri || columns <= 0 || inners <= 0) return fail(TLLM_ERR_ARG, "tllm_weight_create_cpu_format: bad argument");
@@ -502,6 +573,7 @@ int tllm_weight_destroy(tllm_weight* w) {
     cudaFree(w->d_status);
     cudaFree(w->d_x);
     cudaFree(w->d_y);
+    cudaFree(w->d_bias);
     if (w->h_pin) cudaFreeHost(w->h_pin);
     if (w->h_status) cudaFreeHost(w->h_status);
     if (w->own_stream) cudaStreamDestroy(w->own_stream);
@@ -511,34 +583,23 @@ int tllm_weight_destroy(tllm_weight* w) {
 
 int tllm_weight_get_info(const tllm_weight* w, tllm_weight_info* info) {
     if (!w || !info) return fail(TLLM_ERR_ARG, "tllm_weight_get_info: NULL");
-    const TsLayout& L = w->lay;
-    info->inners = L.inners;
-    info->columns = L.columns;
-    info->tile_rows = L.tile_rows;
-    info->tiles = L.tiles;
-    info->col_blocks = L.col_blocks;
-    info->k_splits = L.k_splits;
-    info->tiles_per_cta = L.tiles_per_cta;
-    info->num_ctas = L.num_ctas;
-    info->lanes_per_list = L.lanes_per_list;
+    std::memset(info, 0, sizeof *info);
+    bs_fill_info(w->lay, info);
     info->max_rows = w->max_rows;
-    info->nnz = L.nnz;
     info->stream_bytes = (int64_t)w->stream_bytes;
     info->meta_bytes = (int64_t)w->meta_bytes;
     info->scratch_bytes = (int64_t)w->scratch_bytes;
-    info->algorithmic_bytes = 2 * L.nnz + 16 * (int64_t)L.columns * ((L.inners + 511) / 512);
     info->bit_tile_bytes = (int64_t)w->bits_bytes;
     info->scale = w->scale;
     return TLLM_OK;
 }
 
-// ---- packed-weight files: header, block descriptors, index stream, section tables, bit tiles -------------------
+// ---- packed-weight files: header, column ranges, block descriptors, index stream, block tables, bit tiles ----------
 namespace {
 struct WeightFileHeader {
-    char magic[8];                // "TLLMW001"
-    int32_t inners, columns, tile_rows, tiles, col_blocks, cols_per_block, sub_cols, k_splits, tiles_per_cta, num_ctas, lanes_per_list,
-        max_rows, mm_n_tiles, mm_kb;
-    int64_t nnz, total_vecs, stream_elems, meta_words, bits_words;
+    char magic[8];                // "TLLMW002"
+    int32_t inners, columns, tile_rows, tiles, col_blocks, k_splits, tiles_per_cta, num_ctas, max_cols_per_block, max_rows, mm_n_tiles, mm_kb;
+    int64_t nnz, total_vecs, units, meta_words, bits_words;
     float scale;
     int32_t reserved[7];
 };
@@ -548,14 +609,14 @@ bool write_exact(FILE* f, const void* p, size_t n) { return n == 0 || fwrite(p, 
 
 int tllm_weight_save(const tllm_weight* w, const char* path) {
     if (!w || !path) return fail(TLLM_ERR_ARG, "tllm_weight_save: NULL argument");
-    const TsLayout& L = w->lay;
+    const BsLayout& L = w->lay;
     WeightFileHeader h{};
-    std::memcpy(h.magic, "TLLMW001", 8);
+    std::memcpy(h.magic, "TLLMW002", 8);
     h.inners = L.inners, h.columns = L.columns, h.tile_rows = L.tile_rows, h.tiles = L.tiles, h.col_blocks = L.col_blocks;
-    h.cols_per_block = L.cols_per_block, h.sub_cols = L.sub_cols, h.k_splits = L.k_splits, h.tiles_per_cta = L.tiles_per_cta;
-    h.num_ctas = L.num_ctas, h.lanes_per_list = L.lanes_per_list, h.max_rows = w->max_rows, h.mm_n_tiles = w->mm_n_tiles, h.mm_kb = w->mm_kb;
-    h.nnz = L.nnz, h.total_vecs = L.total_vecs;
-    h.stream_elems = (int64_t)(w->stream_bytes / sizeof(uint16_t)), h.meta_words = (int64_t)(w->meta_bytes / sizeof(uint32_t));
+    h.k_splits = L.k_splits, h.tiles_per_cta = L.tiles_per_cta, h.num_ctas = L.num_ctas, h.max_cols_per_block = L.max_cols_per_block;
+    h.max_rows = w->max_rows, h.mm_n_tiles = w->mm_n_tiles, h.mm_kb = w->mm_kb;
+    h.nnz = L.nnz, h.total_vecs = L.total_vecs, h.units = L.units;
+    h.meta_words = (int64_t)(w->meta_bytes / sizeof(uint32_t));
     h.bits_words = (int64_t)(w->bits_bytes / sizeof(uint32_t));
     h.scale = w->scale;
     std::vector<unsigned char> stream(w->stream_bytes), meta(w->meta_bytes), bits(w->bits_bytes);
@@ -568,8 +629,9 @@ int tllm_weight_save(const tllm_weight* w, const char* path) {
     CU_TRY(cudaSetDevice(prev));
     FILE* f = fopen(path, "wb");
     if (!f) return fail(TLLM_ERR_ARG, "tllm_weight_save: cannot open %s for writing", path);
-    const bool ok = write_exact(f, &h, sizeof h) && write_exact(f, L.cta.data(), L.cta.size() * sizeof(TsCtaDesc)) &&
-                    write_exact(f, stream.data(), stream.size()) && write_exact(f, meta.data(), meta.size()) && write_exact(f, bits.data(), bits.size());
+    const bool ok = write_exact(f, &h, sizeof h) && write_exact(f, L.col_start.data(), L.col_start.size() * sizeof(int32_t)) &&
+                    write_exact(f, L.cta.data(), L.cta.size() * sizeof(TsCtaDesc)) && write_exact(f, stream.data(), stream.size()) &&
+                    write_exact(f, meta.data(), meta.size()) && write_exact(f, bits.data(), bits.size());
     if (fclose(f) != 0 || !ok) return fail(TLLM_ERR_ARG, "tllm_weight_save: short write to %s", path);
     return TLLM_OK;
 }
@@ -580,35 +642,36 @@ int tllm_weight_load(const char* path, tllm_weight** out) {
     FILE* f = fopen(path, "rb");
     if (!f) return fail(TLLM_ERR_ARG, "tllm_weight_load: cannot open %s", path);
     WeightFileHeader h{};
-    TsHostImage img;
+    BsHostImage img;
     std::vector<uint32_t> bits;
-    bool ok = read_exact(f, &h, sizeof h) && std::memcmp(h.magic, "TLLMW001", 8) == 0;
-    ok = ok && h.num_ctas > 0 && h.num_ctas <= TS_MAX_BLOCKS && h.stream_elems >= 0 && h.meta_words >= 0 && h.bits_words >= 0 &&
-         h.stream_elems < ((int64_t)1 << 40) && h.meta_words < ((int64_t)1 << 34) && h.bits_words < ((int64_t)1 << 38);
+    bool ok = read_exact(f, &h, sizeof h) && std::memcmp(h.magic, "TLLMW002", 8) == 0;
+    ok = ok && h.num_ctas > 0 && h.num_ctas <= BS_MAX_BLOCKS && h.col_blocks > 0 && h.col_blocks <= h.num_ctas && h.total_vecs >= 0 && h.meta_words >= 0 &&
+         h.bits_words >= 0 && h.total_vecs < ((int64_t)1 << 32) && h.meta_words < ((int64_t)1 << 34) && h.bits_words < ((int64_t)1 << 38);
     if (ok) {
-        TsLayout& L = img.lay;
+        BsLayout& L = img.lay;
         L.inners = h.inners, L.columns = h.columns, L.tile_rows = h.tile_rows, L.tiles = h.tiles, L.col_blocks = h.col_blocks;
-        L.cols_per_block = h.cols_per_block, L.sub_cols = h.sub_cols, L.k_splits = h.k_splits, L.tiles_per_cta = h.tiles_per_cta;
-        L.num_ctas = h.num_ctas, L.lanes_per_list = h.lanes_per_list, L.nnz = h.nnz, L.total_vecs = h.total_vecs;
+        L.k_splits = h.k_splits, L.tiles_per_cta = h.tiles_per_cta, L.num_ctas = h.num_ctas, L.max_cols_per_block = h.max_cols_per_block;
+        L.nnz = h.nnz, L.total_vecs = h.total_vecs, L.units = h.units;
+        L.col_start.resize((size_t)h.col_blocks + 1);
         L.cta.resize((size_t)h.num_ctas);
-        img.stream.resize((size_t)h.stream_elems);
+        img.stream.resize((size_t)h.total_vecs * 16);
         img.meta.resize((size_t)h.meta_words);
         bits.resize((size_t)h.bits_words);
-        ok = read_exact(f, L.cta.data(), L.cta.size() * sizeof(TsCtaDesc)) && read_exact(f, img.stream.data(), img.stream.size() * sizeof(uint16_t)) &&
-             read_exact(f, img.meta.data(), img.meta.size() * sizeof(uint32_t)) && read_exact(f, bits.data(), bits.size() * sizeof(uint32_t));
+        ok = read_exact(f, L.col_start.data(), L.col_start.size() * sizeof(int32_t)) && read_exact(f, L.cta.data(), L.cta.size() * sizeof(TsCtaDesc)) &&
+             read_exact(f, img.stream.data(), img.stream.size()) && read_exact(f, img.meta.data(), img.meta.size() * sizeof(uint32_t)) &&
+             read_exact(f, bits.data(), bits.size() * sizeof(uint32_t));
     }
     fclose(f);
     if (!ok) return fail(TLLM_ERR_ARG, "tllm_weight_load: %s is not a packed-weight file of this library (or is truncated)", path);
-    if (const char* msg = ts_validate(img)) return fail(TLLM_ERR_ARG, "tllm_weight_load: %s", msg);
+    if (const char* msg = bs_validate(img)) return fail(TLLM_ERR_ARG, "tllm_weight_load: %s", msg);
     const int64_t want_bits = (int64_t)((h.columns + 127) / 128) * ((h.inners + 63) / 64) * 128 * 4;
     if (h.bits_words != 0 && (h.bits_words != want_bits || h.mm_n_tiles != (h.columns + 127) / 128 || h.mm_kb != (h.inners + 63) / 64))
         return fail(TLLM_ERR_ARG, "tllm_weight_load: bit tiles of %s do not match the matrix shape", path);
-    int dev = 0, sms = 0;
-    CU_TRY(cudaGetDevice(&dev));
-    CU_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    if (sms > TS_MAX_CTAS) sms = TS_MAX_CTAS;
+    int sms = 0;
+    int rc = device_sms(&sms);
+    if (rc) return rc;
     tllm_weight* w = new tllm_weight();
-    int rc = upload(w, img, h.scale, h.max_rows > 0 && h.max_rows <= 16 ? h.max_rows : 16);
+    rc = upload(w, img, h.scale, h.max_rows > 0 && h.max_rows <= 4 ? h.max_rows : 4);
     if (rc == TLLM_OK && h.bits_words) {
         w->mm_n_tiles = h.mm_n_tiles;
         w->mm_kb = h.mm_kb;
@@ -628,12 +691,6 @@ int tllm_weight_set_scale(tllm_weight* w, float scale) {
     return TLLM_OK;
 }
 
-int tllm_weight_set_trace(tllm_weight* w, void* device_buffer) {
-    if (!w) return fail(TLLM_ERR_ARG, "tllm_weight_set_trace: NULL");
-    w->d_trace = (long long*)device_buffer;
-    return TLLM_OK;
-}
-
 int tllm_weight_check(tllm_weight* w) {
     if (!w) return fail(TLLM_ERR_ARG, "tllm_weight_check: NULL");
     int st = 0;
@@ -643,7 +700,7 @@ int tllm_weight_check(tllm_weight* w) {
         cudaMemset(w->d_counters, 0, (size_t)w->lay.col_blocks * sizeof(unsigned int));
         if (w->d_mm_counters) cudaMemset(w->d_mm_counters, 0, (size_t)w->mm_n_tiles * 4 * sizeof(unsigned int));
         return fail(TLLM_ERR_KERNEL, "a bounded wait ran out inside the kernel (code %d: %s)", st,
-                    st == MM_ERR_WAIT ? "tensor-core pipeline stalled" : st == TS_ERR_X_WAIT ? "activation tile never arrived" : "unit table never arrived");
+                    st == MM_ERR_WAIT ? "tensor-core pipeline stalled" : "block table never arrived");
     }
     return TLLM_OK;
 }
@@ -652,29 +709,26 @@ int tllm_spmm(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows
     if (!w || !X || !Y) return fail(TLLM_ERR_ARG, "tllm_spmm: NULL pointer");
     if (rows <= 0) return fail(TLLM_ERR_ARG, "tllm_spmm: rows must be positive");
     if (x_layout != TLLM_ROW_MAJOR && x_layout != TLLM_COL_MAJOR) return fail(TLLM_ERR_ARG, "tllm_spmm: bad x_layout");
-    const int rc = check_types(x_dtype, y_dtype, "tllm_spmm");
+    int rc = check_types(x_dtype, y_dtype, "tllm_spmm");
     if (rc) return rc;
-    const TsLayout& L = w->lay;
-    const size_t xe = dtype_size(x_dtype), ye = dtype_size(y_dtype);
+    rc = check_device(w, "tllm_spmm");
+    if (rc) return rc;
+    const BsLayout& L = w->lay;
     const int x_ld = x_layout == TLLM_ROW_MAJOR ? L.inners : rows;
     if (mm_usable(w, X, x_dtype, x_layout, x_ld, rows))
         return run_mm(w, X, x_dtype, x_ld, rows, Y, y_dtype, L.columns, 0, w->scale, 0.f, (cudaStream_t)stream);
-    for (int r0 = 0; r0 < rows; r0 += w->max_rows) {
-        const int m = rows - r0 < w->max_rows ? rows - r0 : w->max_rows;
-        const char* xp = (const char*)X + (x_layout == TLLM_ROW_MAJOR ? (size_t)r0 * L.inners : (size_t)r0) * xe;
-        char* yp = (char*)Y + (size_t)r0 * L.columns * ye;
-        const int r = run_ts(w, xp, x_dtype, x_layout, x_ld, m, yp, y_dtype, L.columns, 0, w->scale, 0.f, (cudaStream_t)stream);
-        if (r) return r;
-    }
-    return TLLM_OK;
+    return run_gather(w, X, x_dtype, x_layout, x_ld, rows, Y, y_dtype, L.columns, 0, w->scale, 0.f, Scratch{w->d_partial, w->d_counters},
+                      (cudaStream_t)stream);
 }
 
-int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y, int y_dtype, int y_layout) {
+int tllm_spmm_host_bias(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, const void* bias, void* Y, int y_dtype, int y_layout) {
     if (!w || !X || !Y) return fail(TLLM_ERR_ARG, "tllm_spmm_host: NULL pointer");
     if (rows <= 0) return fail(TLLM_ERR_ARG, "tllm_spmm_host: rows must be positive");
-    const int rc = check_types(x_dtype, y_dtype, "tllm_spmm_host");
+    int rc = check_types(x_dtype, y_dtype, "tllm_spmm_host");
     if (rc) return rc;
-    const TsLayout& L = w->lay;
+    rc = check_device(w, "tllm_spmm_host");
+    if (rc) return rc;
+    const BsLayout& L = w->lay;
     const size_t xb = (size_t)rows * L.inners * dtype_size(x_dtype), yb = (size_t)rows * L.columns * dtype_size(y_dtype);
     if (!w->own_stream) CU_TRY(cudaStreamCreateWithFlags(&w->own_stream, cudaStreamNonBlocking));
     if (!w->h_status) CU_TRY(cudaMallocHost((void**)&w->h_status, sizeof(int)));
@@ -683,8 +737,17 @@ int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int
     r = ensure(&w->d_y, &w->y_cap, yb, false);
     if (r) return r;
     CU_TRY(cudaMemcpyAsync(w->d_x, X, xb, cudaMemcpyHostToDevice, w->own_stream));
+    if (bias) {
+        r = ensure(&w->d_bias, &w->bias_cap, (size_t)L.columns * dtype_size(y_dtype), false);
+        if (r) return r;
+        CU_TRY(cudaMemcpyAsync(w->d_bias, bias, (size_t)L.columns * dtype_size(y_dtype), cudaMemcpyHostToDevice, w->own_stream));
+    }
     r = tllm_spmm(w, w->d_x, x_dtype, x_layout, rows, w->d_y, y_dtype, w->own_stream);
     if (r) return r;
+    if (bias) {
+        r = add_bias(w->d_y, w->d_bias, y_dtype, rows, L.columns, w->own_stream);
+        if (r) return r;
+    }
     if (y_layout == TLLM_ROW_MAJOR) {
         CU_TRY(cudaMemcpyAsync(Y, w->d_y, yb, cudaMemcpyDeviceToHost, w->own_stream));
         CU_TRY(cudaMemcpyAsync(w->h_status, w->d_status, sizeof(int), cudaMemcpyDeviceToHost, w->own_stream));
@@ -705,6 +768,10 @@ int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int
     return *w->h_status ? tllm_weight_check(w) : TLLM_OK;
 }
 
+int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows, void* Y, int y_dtype, int y_layout) {
+    return tllm_spmm_host_bias(w, X, x_dtype, x_layout, rows, nullptr, Y, y_dtype, y_layout);
+}
+
 }  // extern "C"
 
 // ------------------------------------------------------------------------------------------------------
@@ -714,13 +781,15 @@ int tllm_spmm_host(tllm_weight* w, const void* X, int x_dtype, int x_layout, int
 // at start-up and is policed for late cudaMalloc calls, code that executes under a framework allocator it
 // must not bypass, or a latency-critical path where an allocation (which may synchronise the device) is not
 // acceptable.  tllm_spmm itself allocates nothing either, but the handle it uses had its split-K scratch
-// allocated with cudaMalloc when it was created.  This entry point does not use that scratch: partial sums,
-// arrival counters and the status word live in the fixed array below, which every GPU that loads this
-// library carries until the process exits.  Its size is the limit on what one call may ask for.
+// allocated with cudaMalloc when it was created.  This entry point does not use that scratch: partial sums
+// and arrival counters live in the fixed array below, which every GPU that loads this library carries until
+// the process exits.  Its size is the limit on what one call may ask for.  (The 4-byte status word stays the
+// handle's own -- it exists since the handle was created -- so that tllm_weight_check reports a kernel that
+// gave up on a wait on this path as on every other.)
 // ------------------------------------------------------------------------------------------------------
 #define TLLM_STATIC_SCRATCH_CELLS (1u << 20)   // 4-byte partial sums: k_splits * rows_per_launch * columns must fit
-#define TLLM_STATIC_COUNTERS 256u
-#define TLLM_STATIC_SCRATCH_BYTES (TLLM_STATIC_SCRATCH_CELLS * 4u + TLLM_STATIC_COUNTERS * 4u + 256u)
+#define TLLM_STATIC_COUNTERS 4096u
+#define TLLM_STATIC_SCRATCH_BYTES (TLLM_STATIC_SCRATCH_CELLS * 4u + TLLM_STATIC_COUNTERS * 4u)
 
 static __device__ __align__(256) unsigned char g_static_scratch[TLLM_STATIC_SCRATCH_BYTES];
 
@@ -753,9 +822,11 @@ extern "C" int tllm_spmm_static_scratch(tllm_weight* w, const void* X, int x_dty
     if (x_layout != TLLM_ROW_MAJOR && x_layout != TLLM_COL_MAJOR) return fail(TLLM_ERR_ARG, "tllm_spmm_static_scratch: bad x_layout");
     int rc = check_types(x_dtype, y_dtype, "tllm_spmm_static_scratch");
     if (rc) return rc;
-    const TsLayout& L = w->lay;
+    rc = check_device(w, "tllm_spmm_static_scratch");
+    if (rc) return rc;
+    const BsLayout& L = w->lay;
     const int per_launch = rows < w->max_rows ? rows : w->max_rows;
-    const uint64_t cells = (uint64_t)L.k_splits * (uint64_t)per_launch * (uint64_t)L.columns;
+    const uint64_t cells = L.k_splits > 1 ? (uint64_t)L.k_splits * (uint64_t)per_launch * (uint64_t)L.columns : 0;
     if (cells > TLLM_STATIC_SCRATCH_CELLS)
         return fail(TLLM_ERR_ARG,
                     "tllm_spmm_static_scratch: %d K-splits x %d rows x %d columns = %llu partial sums exceed the built-in scratch of %u; "
@@ -767,55 +838,12 @@ extern "C" int tllm_spmm_static_scratch(tllm_weight* w, const void* X, int x_dty
     if (rc) return rc;
     unsigned char* scratch = (unsigned char*)base;
     unsigned int* counters = (unsigned int*)(scratch + (size_t)TLLM_STATIC_SCRATCH_CELLS * 4u);
-    int* status = (int*)(scratch + (size_t)TLLM_STATIC_SCRATCH_CELLS * 4u + (size_t)TLLM_STATIC_COUNTERS * 4u);
     cudaStream_t st = (cudaStream_t)stream;
     // The array keeps whatever the previous call left.  Partial sums are overwritten before they are read;
-    // the counters and the status word must start at zero, so they are cleared here, in stream order.
-    CU_TRY(cudaMemsetAsync(counters, 0, (size_t)TLLM_STATIC_COUNTERS * 4u + 256u, st));
-    const size_t xe = dtype_size(x_dtype), ye = dtype_size(y_dtype);
+    // the counters must start at zero, so they are cleared here, in stream order.
+    CU_TRY(cudaMemsetAsync(counters, 0, (size_t)TLLM_STATIC_COUNTERS * 4u, st));
     const int x_ld = x_layout == TLLM_ROW_MAJOR ? L.inners : rows;
-    for (int r0 = 0; r0 < rows; r0 += w->max_rows) {
-        const int m = rows - r0 < w->max_rows ? rows - r0 : w->max_rows;
-        const char* xp = (const char*)X + (x_layout == TLLM_ROW_MAJOR ? (size_t)r0 * L.inners : (size_t)r0) * xe;
-        TsParams p{};
-        p.stream = w->d_stream;
-        p.meta = w->d_meta;
-        p.X = xp;
-        p.Y = (char*)Y + (size_t)r0 * L.columns * ye;
-        p.partial = scratch;
-        p.counters = counters;
-        p.status = status;
-        p.trace = nullptr;
-        p.l2_mode = 1;
-        p.x_dtype = x_dtype;
-        p.x_layout = x_layout;
-        p.y_dtype = y_dtype;
-        p.M = m;
-        p.K = L.inners;
-        p.N = L.columns;
-        p.T = L.tile_rows;
-        p.tiles = L.tiles;
-        p.col_blocks = L.col_blocks;
-        p.cols_per_block = L.cols_per_block;
-        p.sub_cols = L.sub_cols;
-        p.k_splits = L.k_splits;
-        p.tiles_per_cta = L.tiles_per_cta;
-        int lg = 0;
-        while ((1 << lg) < L.lanes_per_list) ++lg;
-        p.lpl_log2 = lg;
-        p.epilogue = 0;
-        p.y_ld = L.columns;
-        p.x_ld = x_ld;
-        p.scale = w->scale;
-        p.scale2 = 0.f;
-        p.x_tma = x_layout == TLLM_ROW_MAJOR && ((uintptr_t)xp % 16 == 0) && ((size_t)x_ld * xe % 16 == 0) && ((size_t)L.tile_rows * xe % 16 == 0) &&
-                  ((size_t)L.inners * xe % 16 == 0);
-        p.cta_ext = w->d_cta;
-    std::memcpy(p.cta, L.cta.data(), sizeof(TsCtaDesc) * (size_t)(L.num_ctas < TS_MAX_CTAS ? L.num_ctas : TS_MAX_CTAS));
-        rc = x_dtype == TLLM_I8 ? dispatch_ts<int>(p, L.num_ctas, TS_SMEM_TOTAL, st) : dispatch_ts<float>(p, L.num_ctas, TS_SMEM_TOTAL, st);
-        if (rc) return rc;
-    }
-    return TLLM_OK;
+    return run_gather(w, X, x_dtype, x_layout, x_ld, rows, Y, y_dtype, L.columns, 0, w->scale, 0.f, Scratch{scratch, counters}, st);
 }
 
 extern "C" {
@@ -841,7 +869,6 @@ int tllm_mlp_create(const int8_t* w_gate, const int8_t* w_up, const int8_t* w_do
     m->s_up = s_up;
     int rc = tllm_weight_create_dense(gu.data(), hidden, 2 * intermediate, 1.f, opts, &m->gate_up);
     if (rc == TLLM_OK) rc = tllm_weight_create_dense(w_down, intermediate, hidden, s_down, opts, &m->down);
-    if (rc == TLLM_OK && (m->gate_up->lay.cols_per_block & 1)) rc = fail(TLLM_ERR_ARG, "tllm_mlp_create: internal: odd column block");
     if (rc == TLLM_OK) {
         m->h_cap = (size_t)16 * intermediate * 4;
         cudaError_t e = cudaMalloc(&m->d_h, m->h_cap);
@@ -860,6 +887,8 @@ int tllm_mlp_destroy(tllm_mlp* m) {
     tllm_weight_destroy(m->gate_up);
     tllm_weight_destroy(m->down);
     cudaFree(m->d_h);
+    cudaFree(m->d_x);
+    cudaFree(m->d_y);
     delete m;
     return TLLM_OK;
 }
@@ -868,26 +897,48 @@ int tllm_mlp_forward(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y,
     if (!m || !X || !Y) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: NULL pointer");
     if (rows <= 0) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: rows must be positive");
     if (x_dtype != TLLM_F32 && x_dtype != TLLM_F16 && x_dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: unsupported dtype");
-    if (!H && rows > 16) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: pass H for more than 16 rows");
-    const size_t e = dtype_size(x_dtype);
+    if (!H && (size_t)rows * m->inter * dtype_size(x_dtype) > m->h_cap) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: pass H for more than 16 rows");
+    int rc = check_device(m->gate_up, "tllm_mlp_forward");
+    if (rc) return rc;
     char* h = (char*)(H ? H : m->d_h);
     cudaStream_t st = (cudaStream_t)stream;
-    const int mr = m->gate_up->max_rows;
     if (mm_usable(m->gate_up, X, x_dtype, TLLM_ROW_MAJOR, m->hidden, rows) && mm_usable(m->down, h, x_dtype, TLLM_ROW_MAJOR, m->inter, rows)) {
-        int rc = run_mm(m->gate_up, X, x_dtype, m->hidden, rows, h, x_dtype, m->inter, 1, m->s_gate, m->s_up, st);
+        rc = run_mm(m->gate_up, X, x_dtype, m->hidden, rows, h, x_dtype, m->inter, 1, m->s_gate, m->s_up, st);
         if (rc) return rc;
         return run_mm(m->down, h, x_dtype, m->inter, rows, Y, x_dtype, m->hidden, 0, m->down->scale, 0.f, st);
     }
-    for (int r0 = 0; r0 < rows; r0 += mr) {
-        const int mm = rows - r0 < mr ? rows - r0 : mr;
-        int rc = run_ts(m->gate_up, (const char*)X + (size_t)r0 * m->hidden * e, x_dtype, TLLM_ROW_MAJOR, m->hidden, mm,
-                        h + (size_t)r0 * m->inter * e, x_dtype, m->inter, 1, m->s_gate, m->s_up, st);
-        if (rc) return rc;
-        rc = run_ts(m->down, h + (size_t)r0 * m->inter * e, x_dtype, TLLM_ROW_MAJOR, m->inter, mm, (char*)Y + (size_t)r0 * m->hidden * e,
-                    x_dtype, m->hidden, 0, m->down->scale, 0.f, st);
-        if (rc) return rc;
-    }
-    return TLLM_OK;
+    rc = run_gather(m->gate_up, X, x_dtype, TLLM_ROW_MAJOR, m->hidden, rows, h, x_dtype, m->inter, 1, m->s_gate, m->s_up,
+                    Scratch{m->gate_up->d_partial, m->gate_up->d_counters}, st);
+    if (rc) return rc;
+    return run_gather(m->down, h, x_dtype, TLLM_ROW_MAJOR, m->inter, rows, Y, x_dtype, m->hidden, 0, m->down->scale, 0.f,
+                      Scratch{m->down->d_partial, m->down->d_counters}, st);
+}
+
+int tllm_mlp_forward_host(tllm_mlp* m, void* X, int x_dtype, int rows, void* H) {
+    if (!m || !X) return fail(TLLM_ERR_ARG, "tllm_mlp_forward_host: NULL pointer");
+    if (rows <= 0) return fail(TLLM_ERR_ARG, "tllm_mlp_forward_host: rows must be positive");
+    if (x_dtype != TLLM_F32 && x_dtype != TLLM_F16 && x_dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "tllm_mlp_forward_host: unsupported dtype");
+    tllm_weight* w = m->gate_up;
+    int rc = check_device(w, "tllm_mlp_forward_host");
+    if (rc) return rc;
+    const size_t e = dtype_size(x_dtype), xb = (size_t)rows * m->hidden * e, hb = (size_t)rows * m->inter * e;
+    if (!w->own_stream) CU_TRY(cudaStreamCreateWithFlags(&w->own_stream, cudaStreamNonBlocking));
+    if (!w->h_status) CU_TRY(cudaMallocHost((void**)&w->h_status, sizeof(int)));
+    rc = ensure(&m->d_x, &m->x_cap, xb, false);
+    if (rc) return rc;
+    rc = ensure(&m->d_y, &m->y_cap, xb, false);
+    if (rc) return rc;
+    rc = ensure(&m->d_h, &m->h_cap, hb, false);
+    if (rc) return rc;
+    CU_TRY(cudaMemcpyAsync(m->d_x, X, xb, cudaMemcpyHostToDevice, w->own_stream));
+    rc = tllm_mlp_forward(m, m->d_x, x_dtype, rows, m->d_y, m->d_h, w->own_stream);
+    if (rc) return rc;
+    CU_TRY(cudaMemcpyAsync(X, m->d_y, xb, cudaMemcpyDeviceToHost, w->own_stream));
+    if (H) CU_TRY(cudaMemcpyAsync(H, m->d_h, hb, cudaMemcpyDeviceToHost, w->own_stream));
+    CU_TRY(cudaMemcpyAsync(w->h_status, w->d_status, sizeof(int), cudaMemcpyDeviceToHost, w->own_stream));
+    CU_TRY(cudaStreamSynchronize(w->own_stream));
+    if (*w->h_status) return tllm_weight_check(w);
+    return tllm_weight_check(m->down);
 }
 
 int tllm_mlp_get_info(const tllm_mlp* m, tllm_weight_info* gate_up, tllm_weight_info* down) {

@@ -385,7 +385,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) mma_spmm_kernel(const __grid_co
             for (int c16 = 0; c16 < Nt; c16 += 16) {
                 uint32_t v[16];
                 tmem_ld16(taddr + (uint32_t)c16, v);
-                if (full && p.epilogue == 0 && p.y_dtype != TLLM_F32 && !(p.y_ld & 1) && nt * MM_TILE_N + MM_TILE_N <= p.N) {
+                if (full && p.epilogue == 0 && p.y_dtype != TLLM_F32 && !(p.y_ld & 1) && ((uintptr_t)p.Y & 3u) == 0 && nt * MM_TILE_N + MM_TILE_N <= p.N) {
                     // 16-bit outputs: neighbouring lanes trade one value per pair of rows, so that every lane
                     // writes two adjacent columns of one row with a single 4-byte store
 #pragma unroll

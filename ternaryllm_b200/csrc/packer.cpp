@@ -1,5 +1,5 @@
 // packer.cpp -- host-side format work: the reference's three packers behind the C ABI, decoders for every
-// reference weight format, and the packer of the library's own tile-stream format.
+// reference weight format, the ternarizer and the bit-tile packer (the bank-stream packer is bstream_pack.cpp).
 //
 // Replaces ternaryLLM_GPU/csrc/ter_spmm_wrapper.cu:9-315 (convert_to_ter_csc, convert_to_ter_tiled_csc,
 // convert_to_ter_tiled_mcsc, inter_tile_swizzle) and consumes what ternaryLLM_CPU/src/TCSC.hpp:6-409
@@ -13,43 +13,15 @@
 #include <vector>
 
 #include "../../include/tllm.h"
-#include "tstream_format.h"
+#include "column_lists.h"
+#include "bstream_format.h"
 #include "util.h"
 
 namespace {
 
-inline int tiles_of(int inners, int tile) { return (inners + tile - 1) / tile; }
+using tllm::ColumnLists;
 
-// Column-major view of a row-major ternary matrix: for every column the ascending row ids of the +1 and
-// of the -1 entries.  Built with a counting pass and a scatter pass so that the matrix is read row by row.
-template <typename WT>
-struct ColumnLists {
-    std::vector<int64_t> pos_ptr, neg_ptr;   // columns+1
-    std::vector<int32_t> pos_row, neg_row;
-    ColumnLists(const WT* w, int inners, int columns) : pos_ptr(columns + 1, 0), neg_ptr(columns + 1, 0) {
-        for (int k = 0; k < inners; ++k) {
-            const WT* row = w + (size_t)k * columns;
-            for (int n = 0; n < columns; ++n) {
-                pos_ptr[n + 1] += row[n] > 0;
-                neg_ptr[n + 1] += row[n] < 0;
-            }
-        }
-        for (int n = 0; n < columns; ++n) {
-            pos_ptr[n + 1] += pos_ptr[n];
-            neg_ptr[n + 1] += neg_ptr[n];
-        }
-        pos_row.resize(pos_ptr[columns]);
-        neg_row.resize(neg_ptr[columns]);
-        std::vector<int64_t> pc(pos_ptr.begin(), pos_ptr.end() - 1), nc(neg_ptr.begin(), neg_ptr.end() - 1);
-        for (int k = 0; k < inners; ++k) {
-            const WT* row = w + (size_t)k * columns;
-            for (int n = 0; n < columns; ++n) {
-                if (row[n] > 0) pos_row[pc[n]++] = k;
-                else if (row[n] < 0) neg_row[nc[n]++] = k;
-            }
-        }
-    }
-};
+inline int tiles_of(int inners, int tile) { return (inners + tile - 1) / tile; }
 
 bool ternary_only(const int32_t* w, size_t n) {
     for (size_t i = 0; i < n; ++i)
@@ -375,285 +347,6 @@ const char* decode_cpu_format(int kind, int group, int chunk, const int32_t* met
 
 }  // namespace tllm
 
-// ------------------------------------------------------------------------------------------------------
-// Tile-stream packer
-// ------------------------------------------------------------------------------------------------------
-namespace {
-
-int pow2_ceil(int v) {
-    int p = 1;
-    while (p < v) p *= 2;
-    return p;
-}
-
-struct ListRef {
-    int col;        // column within the sub-block
-    int sign;       // 0: +1 list, 1: -1 list
-    const int32_t* first;
-    int n;          // ids
-    int nvec() const { return (n + TS_IDS_PER_VEC - 1) / TS_IDS_PER_VEC; }
-};
-
-// upper bound of the table words of one block (a list has at most tile_rows/8 + 1 vectors)
-size_t meta_words_of(int ncols, int sub_cols, int T, int ntiles) {
-    size_t words = 0;
-    for (int c = 0; c < ncols; c += sub_cols) words += TS_SEC_HEADER + (size_t)(T / TS_IDS_PER_VEC + 2) + 2 * (size_t)std::min(sub_cols, ncols - c);
-    return words * (size_t)ntiles;
-}
-
-}  // namespace
-
-const char* ts_pack_dense(const int8_t* w, int inners, int columns, const tllm_pack_opts* opts, int num_sms,
-                          TsHostImage* out) {
-    if (!w || inners <= 0 || columns <= 0) return "pack: bad matrix shape";
-    if ((int64_t)inners * columns > ((int64_t)1 << 40)) return "pack: matrix too large";
-    tllm_pack_opts o{};
-    if (opts) o = *opts;
-    int T = o.tile_rows > 0 ? o.tile_rows : TS_MAX_TILE_ROWS;
-    if (T > TS_MAX_TILE_ROWS || T % 8) return "pack: tile_rows must be a multiple of 8 and at most 1024";
-    if (T > inners) T = (inners + 7) / 8 * 8;
-    int ctas = o.num_ctas > 0 ? o.num_ctas : num_sms;
-    if (ctas <= 0 || ctas > TS_MAX_CTAS) return "pack: num_ctas out of range";
-    int lpl = o.lanes_per_list > 0 ? o.lanes_per_list : 1;   // 0: chosen below, once the column blocks are known
-    if (lpl < 1 || lpl > 16 || (lpl & (lpl - 1))) return "pack: lanes_per_list must be 1, 2, 4, 8 or 16";
-    const int tiles = tiles_of(inners, T);
-
-    // ---- schedule: k_splits x col_blocks blocks, each block owns tiles_per_cta tiles of one column block
-    int best_tpc = 0, best_nb = 1;
-    double best_cost = 1e300;
-    for (int tpc = 1; tpc <= tiles; ++tpc) {
-        const int splits = (tiles + tpc - 1) / tpc;
-        if (o.k_splits > 0 && tpc != (tiles + o.k_splits - 1) / o.k_splits) continue;
-        // column blocks hold an even number of columns, so that (gate, up) column pairs never straddle one
-        // (and, when wide enough, a multiple of 16 columns = 32 lists, so that no unit is left with idle lanes)
-        auto cols_for = [&](int blocks) {
-            const int c = (columns + blocks - 1) / blocks;
-            return c >= 64 ? (c + 15) & ~15 : (c + 1) & ~1;
-        };
-        // one wave of blocks when the per-block section table fits its shared-memory budget; wide matrices
-        // take several full waves instead
-        for (int wv = 1; wv <= 64; ++wv) {
-            int nb = std::min(ctas * wv / splits, (columns + 1) / 2);
-            if (nb < 1) nb = 1;
-            const int bc = cols_for(nb);
-            if (meta_words_of(bc, std::min(bc, TS_MAX_SUB_COLS), T, tpc) * 4 + 16 > TS_MAX_META_BYTES && bc > 2) continue;
-            nb = (columns + bc - 1) / bc;
-            if ((int64_t)nb * splits > TS_MAX_BLOCKS) break;
-            // time ~ waves * (work of the busiest block + one activation-table fill per tile it owns)
-            // (a fill takes about as long as streaming the lists of 32 Ki matrix entries at 75 % sparsity)
-            const double waves = (nb * splits + ctas - 1) / ctas;
-            const double work = (double)tpc * bc * T;
-            const double fill = (double)tpc * 32768.0;
-            const double cost = waves * (work + fill);
-            if (cost < best_cost) {
-                best_cost = cost;
-                best_tpc = tpc;
-                best_nb = nb;
-            }
-            break;   // more waves of smaller blocks only add fills
-        }
-    }
-    if (best_tpc == 0) return "pack: no schedule fits (matrix too wide for the block budget)";
-    TsLayout& L = out->lay;
-    L = TsLayout{};
-    L.inners = inners;
-    L.columns = columns;
-    L.tile_rows = T;
-    L.tiles = tiles;
-    L.tiles_per_cta = best_tpc;
-    L.k_splits = (tiles + best_tpc - 1) / best_tpc;
-    {
-        const int c = (columns + best_nb - 1) / best_nb;
-        L.cols_per_block = c >= 64 ? (c + 15) & ~15 : (c + 1) & ~1;
-    }
-    L.col_blocks = (columns + L.cols_per_block - 1) / L.cols_per_block;
-    L.num_ctas = L.col_blocks * L.k_splits;
-    L.cta.assign((size_t)L.num_ctas, TsCtaDesc{});
-    L.sub_cols = std::min(L.cols_per_block, TS_MAX_SUB_COLS);
-    if (o.lanes_per_list <= 0) {
-        // One lane per list keeps padding and shuffles lowest.  Narrow column blocks have too few lists to
-        // fill the lanes of a unit or to give every warp a unit: there several lanes share a list.
-        const int nlists = 2 * L.sub_cols;
-        lpl = std::min(16, std::max(1, pow2_ceil((12 * 32 + nlists - 1) / nlists)));
-    }
-    L.lanes_per_list = lpl;
-
-    ColumnLists<int8_t> cl(w, inners, columns);
-    L.nnz = (int64_t)cl.pos_row.size() + (int64_t)cl.neg_row.size();
-
-    out->stream.clear();
-    out->meta.clear();
-    std::vector<ListRef> lists;
-    auto pad_vectors_to = [&](size_t mult) {
-        while ((out->stream.size() / TS_IDS_PER_VEC) % mult) out->stream.insert(out->stream.end(), TS_IDS_PER_VEC, (uint16_t)T);
-    };
-    for (int j = 0; j < L.k_splits; ++j) {
-        for (int b = 0; b < L.col_blocks; ++b) {
-            const int cta = j * L.col_blocks + b;
-            const int c0 = b * L.cols_per_block, c1 = std::min(columns, c0 + L.cols_per_block);
-            const int t0 = j * L.tiles_per_cta, t1 = std::min(tiles, t0 + L.tiles_per_cta);
-            while (out->meta.size() % 4) out->meta.push_back(0);
-            pad_vectors_to(32);
-            TsCtaDesc& d = L.cta[cta];
-            d.stream_off = (uint32_t)(out->stream.size() / TS_IDS_PER_VEC);
-            d.meta_off = (uint32_t)out->meta.size();
-            const size_t base = out->stream.size();
-            for (int t = t0; t < t1; ++t) {
-                const int lo = t * T, hi = lo + T;
-                for (int s0 = c0; s0 < c1; s0 += L.sub_cols) {
-                    const int s1 = std::min(c1, s0 + L.sub_cols);
-                    lists.clear();
-                    for (int c = s0; c < s1; ++c)
-                        for (int sg = 0; sg < 2; ++sg) {
-                            const std::vector<int64_t>& ptr = sg ? cl.neg_ptr : cl.pos_ptr;
-                            const std::vector<int32_t>& rows = sg ? cl.neg_row : cl.pos_row;
-                            const int32_t* first = std::lower_bound(rows.data() + ptr[c], rows.data() + ptr[c + 1], lo);
-                            const int32_t* last = std::lower_bound(first, rows.data() + ptr[c + 1], hi);
-                            lists.push_back(ListRef{c - s0, sg, first, (int)(last - first)});
-                        }
-                    // longest first; ties keep column order, so the layout is a pure function of W
-                    auto steps_of = [&](const ListRef& l) { return (l.nvec() + lpl - 1) / lpl; };
-                    std::stable_sort(lists.begin(), lists.end(), [&](const ListRef& a, const ListRef& b2) { return steps_of(a) > steps_of(b2); });
-                    const int nl = (int)lists.size();
-                    const int ndiag = nl ? steps_of(lists[0]) : 0;
-                    pad_vectors_to(32);
-                    const size_t sec_base = out->stream.size();
-                    out->meta.push_back((uint32_t)((sec_base - base) / TS_IDS_PER_VEC));
-                    out->meta.push_back((uint32_t)ndiag);
-                    out->meta.push_back((uint32_t)nl);
-                    out->meta.push_back(0);
-                    const size_t diag_words = out->meta.size();
-                    out->meta.resize(diag_words + ndiag + 1);
-                    int live = nl;   // lists that still have a vector in this diagonal: a prefix of the sorted order
-                    for (int i = 0; i < ndiag; ++i) {
-                        while (live > 0 && steps_of(lists[live - 1]) <= i) --live;
-                        pad_vectors_to(8);
-                        out->meta[diag_words + i] = (uint32_t)((out->stream.size() - sec_base) / TS_IDS_PER_VEC);
-                        for (int l = 0; l < live; ++l)
-                            for (int jj = 0; jj < lpl; ++jj) {
-                                const int v = i * lpl + jj;
-                                for (int e = 0; e < TS_IDS_PER_VEC; ++e) {
-                                    const int at = v * TS_IDS_PER_VEC + e;
-                                    out->stream.push_back(at < lists[l].n ? (uint16_t)(lists[l].first[at] - lo) : (uint16_t)T);
-                                }
-                            }
-                    }
-                    pad_vectors_to(8);
-                    out->meta[diag_words + ndiag] = (uint32_t)((out->stream.size() - sec_base) / TS_IDS_PER_VEC);
-                    for (const ListRef& l : lists)
-                        out->meta.push_back((uint32_t)(l.col | (l.sign << 15)) | ((uint32_t)steps_of(l) << 16));
-                }
-            }
-            pad_vectors_to(32);
-            d.nvec = (uint32_t)((out->stream.size() - base) / TS_IDS_PER_VEC);
-            while (out->meta.size() % 4) out->meta.push_back(0);
-            d.meta_words = (uint32_t)(out->meta.size() - d.meta_off);
-            if ((size_t)d.meta_words * 4 > TS_MAX_META_BYTES) return "pack: section table exceeds its shared-memory budget";
-        }
-    }
-    L.total_vecs = (int64_t)(out->stream.size() / TS_IDS_PER_VEC);
-    if (L.total_vecs >= ((int64_t)1 << 32)) return "pack: stream exceeds 64 GiB";
-    return nullptr;
-}
-
-namespace {
-
-// Walks every section of an image: f(block descriptor, tile, first column of the sub-block, columns in it, section words)
-template <typename F>
-void for_each_section(const TsHostImage& img, F&& f) {
-    const TsLayout& L = img.lay;
-    for (int j = 0; j < L.k_splits; ++j)
-        for (int b = 0; b < L.col_blocks; ++b) {
-            const TsCtaDesc& d = L.cta[j * L.col_blocks + b];
-            const int c0 = b * L.cols_per_block, c1 = std::min(L.columns, c0 + L.cols_per_block);
-            const int t0 = j * L.tiles_per_cta, t1 = std::min(L.tiles, t0 + L.tiles_per_cta);
-            const uint32_t* sec = img.meta.data() + d.meta_off;
-            for (int t = t0; t < t1; ++t)
-                for (int s0 = c0; s0 < c1; s0 += L.sub_cols) {
-                    const int ns = std::min(L.sub_cols, c1 - s0);
-                    f(d, t, s0, ns, sec);
-                    sec += TS_SEC_HEADER + sec[1] + 1 + sec[2];
-                }
-        }
-}
-
-}  // namespace
-
-void ts_unpack_dense(const TsHostImage& img, int8_t* w) {
-    const TsLayout& L = img.lay;
-    std::memset(w, 0, (size_t)L.inners * L.columns);
-    const int lpl = L.lanes_per_list;
-    for_each_section(img, [&](const TsCtaDesc& d, int t, int s0, int, const uint32_t* sec) {
-        const uint32_t ndiag = sec[1], nl = sec[2];
-        const uint32_t* diag = sec + TS_SEC_HEADER;
-        const uint32_t* lists = diag + ndiag + 1;
-        for (uint32_t l = 0; l < nl; ++l) {
-            const uint32_t tag = lists[l] & 0xffffu, steps = lists[l] >> 16;
-            for (uint32_t i = 0; i < steps; ++i)
-                for (int jj = 0; jj < lpl; ++jj) {
-                    const size_t vec = (size_t)d.stream_off + sec[0] + diag[i] + (size_t)l * lpl + jj;
-                    for (int e = 0; e < TS_IDS_PER_VEC; ++e) {
-                        const int id = img.stream[vec * TS_IDS_PER_VEC + e];
-                        if (id < L.tile_rows && t * L.tile_rows + id < L.inners)
-                            w[(size_t)(t * L.tile_rows + id) * L.columns + s0 + (tag & 0x7fff)] += (tag >> 15) ? -1 : 1;
-                    }
-                }
-        }
-    });
-}
-
-const char* ts_validate(const TsHostImage& img) {
-    const TsLayout& L = img.lay;
-    if (L.num_ctas != L.col_blocks * L.k_splits || L.num_ctas > TS_MAX_BLOCKS || L.cta.size() != (size_t)L.num_ctas) return "validate: block count";
-    if ((L.cols_per_block & 1) || L.sub_cols > TS_MAX_SUB_COLS || L.sub_cols <= 0) return "validate: column block / sub-block size";
-    if (L.sub_cols < L.cols_per_block && (L.sub_cols & 1)) return "validate: odd sub-block";
-    const int lpl = L.lanes_per_list;
-    if (lpl < 1 || lpl > 16 || (lpl & (lpl - 1))) return "validate: lanes per list";
-    for (int i = 0; i < L.num_ctas; ++i) {
-        const TsCtaDesc& d = L.cta[i];
-        if (d.stream_off % 32 || d.nvec % 32 || d.meta_off % 4 || d.meta_words % 4) return "validate: alignment";
-        if ((size_t)(d.stream_off + d.nvec) * TS_IDS_PER_VEC > img.stream.size()) return "validate: stream range";
-        if ((size_t)d.meta_off + d.meta_words > img.meta.size()) return "validate: table range";
-        if ((size_t)d.meta_words * 4 > TS_MAX_META_BYTES) return "validate: table size";
-    }
-    const char* err = nullptr;
-    std::vector<int> seen;
-    for_each_section(img, [&](const TsCtaDesc& d, int, int, int ns, const uint32_t* sec) {
-        if (err) return;
-        const uint32_t ndiag = sec[1], nl = sec[2];
-        if ((size_t)(sec - (img.meta.data() + d.meta_off)) + TS_SEC_HEADER + ndiag + 1 + nl > d.meta_words) { err = "validate: section table overruns the block's table"; return; }
-        if (nl != (uint32_t)(2 * ns)) { err = "validate: list count"; return; }
-        if (sec[0] % 32) err = "validate: section alignment";
-        const uint32_t* diag = sec + TS_SEC_HEADER;
-        const uint32_t* lists = diag + ndiag + 1;
-        if (sec[0] + diag[ndiag] > d.nvec) err = "validate: section data out of the block's range";
-        seen.assign((size_t)2 * ns, 0);
-        uint32_t prev_steps = 0xffffffffu;
-        for (uint32_t l = 0; l < nl; ++l) {
-            const uint32_t tag = lists[l] & 0xffffu, steps = lists[l] >> 16;
-            if (steps > prev_steps) err = "validate: lists not sorted by length";
-            prev_steps = steps;
-            if (steps > ndiag) err = "validate: list longer than the diagonal count";
-            if ((int)(tag & 0x7fff) >= ns) { err = "validate: column tag out of range"; return; }
-            seen[(size_t)2 * (tag & 0x7fff) + (tag >> 15)]++;
-        }
-        for (int v : seen)
-            if (v != 1) err = "validate: a list is missing or duplicated";
-        // every diagonal holds exactly the lists that reach it, starts on 128 bytes and fits before the next one
-        for (uint32_t i = 0; i < ndiag; ++i) {
-            uint32_t live = 0;
-            for (uint32_t l = 0; l < nl; ++l) live += (lists[l] >> 16) > i;
-            if (diag[i] % 8) err = "validate: diagonal alignment";
-            if (diag[i] + live * (uint32_t)lpl > diag[i + 1]) err = "validate: diagonals overlap";
-        }
-        if (nl && ndiag != (lists[0] >> 16)) err = "validate: diagonal count";
-    });
-    if (err) return err;
-    for (uint16_t id : img.stream)
-        if (id > (uint16_t)L.tile_rows) return "validate: row id beyond the zero row";
-    return nullptr;
-}
-
 // ---------------------------------------------------------------------------------------------------
 // float weights -> ternary weights + per-tensor scale (the reference's ternarize_weights is a stub that raises,
 // ternaryLLM_GPU/TernaryLLM/TernaryLinear.py:19-20; this is the threshold rule of ternary weight networks)
@@ -728,14 +421,19 @@ void mm_unpack_bits(const std::vector<uint32_t>& bits, int inners, int columns, 
     }
 }
 
+namespace tllm {
+void bs_fill_info(const BsLayout& L, tllm_weight_info* info);
+}
+
 extern "C" int tllm_pack_roundtrip(const int8_t* w, int inners, int columns, const tllm_pack_opts* opts, int num_sms,
                                    int8_t* w_out, tllm_weight_info* info) {
     if (!w || !w_out || inners <= 0 || columns <= 0 || num_sms <= 0) return tllm::fail(TLLM_ERR_ARG, "tllm_pack_roundtrip: bad argument");
-    TsHostImage img;
-    const char* msg = ts_pack_dense(w, inners, columns, opts, num_sms, &img);
-    if (!msg) msg = ts_validate(img);
+    BsHostImage img;
+    const char* msg = bs_pack_dense(w, inners, columns, opts, num_sms, &img);
+    if (!msg) msg = bs_validate(img);
     if (msg) return tllm::fail(TLLM_ERR_ARG, "%s", msg);
-    ts_unpack_dense(img, w_out);
+    bs_unpack_dense(img, w_out);
+    int64_t bit_bytes = 0;
     {   // the second representation must describe the same matrix
         std::vector<uint32_t> bits;
         int nt = 0, kb = 0;
@@ -743,26 +441,46 @@ extern "C" int tllm_pack_roundtrip(const int8_t* w, int inners, int columns, con
         std::vector<int8_t> back((size_t)inners * columns);
         mm_unpack_bits(bits, inners, columns, back.data());
         if (std::memcmp(back.data(), w, back.size()) != 0) return tllm::fail(TLLM_ERR_ARG, "bit tiles do not reproduce the matrix");
-        if (info) info->bit_tile_bytes = (int64_t)bits.size() * 4;
+        bit_bytes = (int64_t)bits.size() * 4;
     }
     if (info) {
-        const int64_t keep_bits = info->bit_tile_bytes;
-        const TsLayout& L = img.lay;
         std::memset(info, 0, sizeof *info);
-        info->bit_tile_bytes = keep_bits;
-        info->inners = L.inners;
-        info->columns = L.columns;
-        info->tile_rows = L.tile_rows;
-        info->tiles = L.tiles;
-        info->col_blocks = L.col_blocks;
-        info->k_splits = L.k_splits;
-        info->tiles_per_cta = L.tiles_per_cta;
-        info->num_ctas = L.num_ctas;
-        info->lanes_per_list = L.lanes_per_list;
-        info->nnz = L.nnz;
-        info->stream_bytes = (int64_t)img.stream.size() * 2;
+        tllm::bs_fill_info(img.lay, info);
+        info->bit_tile_bytes = bit_bytes;
+        info->stream_bytes = (int64_t)img.stream.size();
         info->meta_bytes = (int64_t)img.meta.size() * 4;
-        info->algorithmic_bytes = 2 * L.nnz + 16 * (int64_t)L.columns * ((L.inners + 511) / 512);
     }
+    return TLLM_OK;
+}
+
+// Host-side check of a packed image given as raw arrays (what a packed-weight file holds): used by tests to show
+// that damaged images are refused before anything is uploaded.
+extern "C" int tllm_pack_corrupt_check(const int8_t* w, int inners, int columns, const tllm_pack_opts* opts, int num_sms, int what, int64_t where,
+                                       uint32_t value) {
+    if (!w || inners <= 0 || columns <= 0 || num_sms <= 0) return tllm::fail(TLLM_ERR_ARG, "tllm_pack_corrupt_check: bad argument");
+    BsHostImage img;
+    const char* msg = bs_pack_dense(w, inners, columns, opts, num_sms, &img);
+    if (!msg) msg = bs_validate(img);
+    if (msg) return tllm::fail(TLLM_ERR_ARG, "%s", msg);
+    BsLayout& L = img.lay;
+    switch (what) {
+        case 0: break;   // untouched: must validate
+        case 1: if (where >= 0 && (size_t)where < img.meta.size()) img.meta[(size_t)where] = value; break;
+        case 2: if (where >= 0 && (size_t)where < img.stream.size()) img.stream[(size_t)where] = (uint8_t)value; break;
+        case 3: L.tile_rows = (int)value; break;
+        case 4: L.tiles = (int)value; break;
+        case 5: L.col_blocks = (int)value; break;
+        case 6: L.k_splits = (int)value; break;
+        case 7: L.tiles_per_cta = (int)value; break;
+        case 8: if (where >= 0 && (size_t)where < L.cta.size()) L.cta[(size_t)where].meta_words = value; break;
+        case 9: if (where >= 0 && (size_t)where < L.cta.size()) L.cta[(size_t)where].stream_off = value; break;
+        case 10: if (where >= 0 && (size_t)where < L.col_start.size()) L.col_start[(size_t)where] = (int32_t)value; break;
+        case 11: L.inners = (int)value; break;
+        case 12: if (where >= 0 && (size_t)where < L.cta.size()) L.cta[(size_t)where].meta_off = value; break;
+        case 13: if (where >= 0 && (size_t)where < L.cta.size()) L.cta[(size_t)where].nvec = value; break;
+        default: return tllm::fail(TLLM_ERR_ARG, "tllm_pack_corrupt_check: unknown field");
+    }
+    msg = bs_validate(img);
+    if (msg) return tllm::fail(TLLM_ERR_ARG, "%s", msg);
     return TLLM_OK;
 }

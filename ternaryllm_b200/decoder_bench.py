@@ -47,7 +47,7 @@ def main():
 
     import torch.distributed as dist
 
-    from bench import make_weight, measured_peak
+    from ternaryllm_b200.synthetic import make_weight, measured_peak
     from ternaryllm_b200 import _lib
     from ternaryllm_b200.tensor_parallel import TernaryDecoderLayerTP
 

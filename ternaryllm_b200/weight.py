@@ -9,8 +9,8 @@ from . import _lib
 from ._lib import PackOpts, WeightInfo, check, lib, np_ptr
 
 
-def _opts(tile_rows=0, num_ctas=0, lanes_per_list=0, max_rows=0, k_splits=0, no_bit_tiles=0):
-    return PackOpts(int(tile_rows), int(num_ctas), int(lanes_per_list), int(max_rows), int(k_splits), int(no_bit_tiles))
+def _opts(tile_rows=0, num_ctas=0, max_rows=0, k_splits=0, no_bit_tiles=0):
+    return PackOpts(int(tile_rows), int(num_ctas), 0, int(max_rows), int(k_splits), int(no_bit_tiles))
 
 
 def _dense_i8(w):
@@ -25,7 +25,7 @@ def _dense_i8(w):
 
 
 class PackedWeight:
-    """A ternary matrix W [inners, columns] packed into the tile-stream format on the current CUDA device."""
+    """A ternary matrix W [inners, columns] packed into the bank-stream format on the current CUDA device."""
 
     def __init__(self, handle, device_index):
         self._h = handle

@@ -108,7 +108,7 @@ def test_ter_spmm_int8(gpu_packers):
 
 
 # ------------------------------------------------------------------------------------------------------
-# tile-stream kernel
+# gather kernel on the bank-stream format
 # ------------------------------------------------------------------------------------------------------
 SHAPES = [
     # K, N, sparsity, pack options
@@ -118,17 +118,21 @@ SHAPES = [
     (1536, 130, 0.9, {}),
     (4096, 344, 0.75, {}),
     (3000, 2, 0.5, {}),
-    (700, 40, 0.7, {"tile_rows": 256}),
-    (700, 40, 0.7, {"tile_rows": 64, "lanes_per_list": 16}),
-    (700, 40, 0.0, {"num_ctas": 3}),                      # dense, several tiles per block
-    (2500, 64, 0.6, {"num_ctas": 2, "lanes_per_list": 1}),
-    (5000, 24, 0.8, {"num_ctas": 1}),                     # one block walks five tiles
+    (700, 40, 0.7, {"tile_rows": 256}),                   # three tiles resident at once (one row), one at a time (four rows)
+    (700, 40, 0.7, {"tile_rows": 64, "k_splits": 1}),     # eleven tiles in one block: several table refills
+    (700, 40, 0.7, {"tile_rows": 64, "k_splits": 4}),     # the same through the split-K hand-over
+    (700, 40, 0.0, {"num_ctas": 3}),                      # dense
+    (2500, 64, 0.6, {"num_ctas": 2, "tile_rows": 512}),
+    (5000, 24, 0.8, {"num_ctas": 1}),                     # one block, two tiles
+    (9000, 36, 0.8, {}),                                  # three tiles, K-split chosen by the packer
+    (4096, 200, 0.97, {"num_ctas": 1}),                   # one warp walks many columns: ring wrap-around and reduce points
     (128, 16, 1.0, {}),                                   # all-zero weight
+    (999, 77, 0.6, {}),                                   # K not a multiple of 16 (no vector loads of X), odd N
 ]
 
 
 @pytest.mark.parametrize("K,N,s,opts", SHAPES)
-def test_tstream_bit_exact_on_integer_activations(K, N, s, opts):
+def test_gather_bit_exact_on_integer_activations(K, N, s, opts):
     rng = np.random.default_rng(K * 31 + N)
     w = random_ternary(rng, K, N, s)
     if N > 12:
@@ -158,7 +162,7 @@ def test_tstream_bit_exact_on_integer_activations(K, N, s, opts):
 
 @pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("M", [1, 4, 16])
-def test_tstream_tolerance_on_gaussian_activations(dtype, M):
+def test_gather_tolerance_on_gaussian_activations(dtype, M):
     rng = np.random.default_rng(M)
     K, N, s = 4096, 688, 0.75
     w = random_ternary(rng, K, N, s)
@@ -308,16 +312,16 @@ def test_fused_mlp(dtype):
 
 
 def test_wide_matrix_runs_as_several_waves_of_blocks():
-    """8192 x 57344 (the fused gate|up width of a 70B-class MLP): the section tables of one wave of blocks would
-    not fit shared memory, so the schedule takes two waves (296 blocks) and the blocks past the first 160 read
-    their descriptors from device memory.  Exact on integer activations, against a dense product on the device."""
-    from bench import make_weight
+    """8192 x 57344 (the fused gate|up width of a 70B-class MLP) packed for 400 thread blocks: more blocks than one
+    wave holds, and the blocks past the first 160 read their descriptors from device memory.  Exact on integer
+    activations, against a dense product on the device."""
+    from ternaryllm_b200.synthetic import make_weight
 
     K, N = 8192, 57344
     w = make_weight(3, K, N, 0.875)
-    pw = PackedWeight.from_dense(w, scale=1.0)
+    pw = PackedWeight.from_dense(w, scale=1.0, num_ctas=400)
     info = pw.info
-    assert info["num_ctas"] > 160 and info["num_ctas"] == info["col_blocks"] * info["k_splits"]
+    assert info["num_ctas"] > 160 and info["num_ctas"] == info["col_blocks"] * info["k_splits"] and info["tiles"] == 2
     rng = np.random.default_rng(3)
     Wd = torch.tensor(w, device=dev()).float()
     for M in (1, 5, 16):

@@ -83,14 +83,14 @@ def _roundtrip(w, **opts):
     K, N = w.shape
     out = np.full_like(w, 7)
     info = _lib.WeightInfo()
-    o = _lib.PackOpts(opts.get("tile_rows", 0), opts.get("num_ctas", 0), opts.get("lanes_per_list", 0), 0, opts.get("k_splits", 0))
+    o = _lib.PackOpts(opts.get("tile_rows", 0), opts.get("num_ctas", 0), opts.get("reserved0", 0), 0, opts.get("k_splits", 0))
     rc = _lib.lib().tllm_pack_roundtrip(_lib.np_ptr(w), K, N, C.byref(o), opts.get("num_sms", 148), _lib.np_ptr(out), C.byref(info))
     return rc, out, info.as_dict()
 
 
 @pytest.mark.parametrize("K,N,s", [(64, 8, 0.5), (1000, 70, 0.75), (2048, 256, 0.5), (4096, 344, 0.75), (1536, 130, 0.9),
-                                   (11008 // 4, 96, 0.6), (33, 5, 0.3), (8, 2, 0.0), (3000, 2, 0.5)])
-def test_tile_stream_roundtrip(K, N, s):
+                                   (11008 // 4, 96, 0.6), (33, 5, 0.3), (8, 2, 0.0), (3000, 2, 0.5), (9000, 37, 0.6)])
+def test_bank_stream_roundtrip(K, N, s):
     rng = np.random.default_rng(K * 7 + N)
     w = random_ternary(rng, K, N, s)
     rc, out, info = _roundtrip(w)
@@ -98,11 +98,13 @@ def test_tile_stream_roundtrip(K, N, s):
     assert np.array_equal(out, w)
     assert info["nnz"] == int((w != 0).sum())
     assert info["num_ctas"] <= 148 and info["num_ctas"] == info["col_blocks"] * info["k_splits"]
+    assert info["tiles"] == -(-K // 4096)
 
 
-def test_tile_stream_storage_overhead_at_benchmark_density():
+def test_bank_stream_storage_at_benchmark_density():
     """A quarter of the Llama-7B up-projection columns packed for a quarter of the SMs has the per-block structure
-    of the full matrix: padding (vector rounding + equalising the sorted lists of a unit) stays below 6 %."""
+    of the full matrix: one byte per non-zero plus padding to whole words, the flag bytes and the tables stay below
+    0.6 of the reference layout's bytes (2 bytes per non-zero + 16 per column and 512-row tile)."""
     rng = np.random.default_rng(0)
     K, N = 4096, 2752
     r = rng.integers(0, 256, size=(K, N), dtype=np.uint8)
@@ -111,20 +113,22 @@ def test_tile_stream_storage_overhead_at_benchmark_density():
     w[r >= 224] = 1
     rc, out, info = _roundtrip(w, num_sms=37)
     assert rc == 0 and np.array_equal(out, w)
-    assert info["lanes_per_list"] == 1 and info["k_splits"] == 4 and info["num_ctas"] == 36 or info["num_ctas"] == 37
-    assert info["stream_bytes"] <= 1.06 * 2 * info["nnz"], info
+    assert info["k_splits"] == 1 and info["num_ctas"] == 37 and info["tiles"] == 1
+    assert info["stream_bytes"] + info["meta_bytes"] <= 0.6 * info["algorithmic_bytes"], info
     assert info["meta_bytes"] <= 0.02 * info["stream_bytes"]
+    # every warp of every block got one unit: the lanes never drift more than a ring apart on random data
+    assert info["units"] == 37 * 8
 
 
-def test_tile_stream_edge_cases():
+def test_bank_stream_edge_cases():
     rng = np.random.default_rng(5)
     w = random_ternary(rng, 700, 40, 0.7)
     w[:, 3] = 0                # empty column
     w[256:512, :] = 0          # empty rows spanning a tile boundary
     w[:, 9] = 1                # dense +1 column
     w[:, 10] = -1              # dense -1 column
-    for opts in (dict(), dict(tile_rows=256), dict(tile_rows=64, lanes_per_list=16), dict(num_ctas=8), dict(num_ctas=1),
-                 dict(lanes_per_list=1), dict(tile_rows=1024, lanes_per_list=2), dict(k_splits=1), dict(tile_rows=128, k_splits=2)):
+    for opts in (dict(), dict(tile_rows=256), dict(tile_rows=64), dict(num_ctas=8), dict(num_ctas=1), dict(tile_rows=32),
+                 dict(tile_rows=1024), dict(k_splits=1), dict(tile_rows=128, k_splits=2), dict(tile_rows=128, k_splits=100)):
         rc, out, info = _roundtrip(w, **opts)
         assert rc == 0, (opts, _lib.lib().tllm_last_error())
         assert np.array_equal(out, w), opts
@@ -134,26 +138,72 @@ def test_tile_stream_edge_cases():
     assert rc == 0 and not out.any() and info["nnz"] == 0
 
 
-def test_tile_stream_rejects_bad_options():
+def test_bank_stream_lanes_that_drift_apart_end_their_unit_early():
+    """All non-zeros of 200 columns in the rows of one lane: that lane's lists are long, the 31 others hold one word
+    per list and run far ahead.  The packer has to cut the columns into units short enough for the 16-slot ring."""
+    K, N = 4096, 200
+    w = np.zeros((K, N), np.int8)
+    w[5::32, :] = 1
+    w[5::64, ::3] = -1
+    rc, out, info = _roundtrip(w, num_ctas=1)
+    assert rc == 0, _lib.lib().tllm_last_error()
+    assert np.array_equal(out, w)
+    assert info["units"] > 8
+
+
+def test_bank_stream_rejects_bad_options():
     w = np.zeros((64, 8), np.int8)
-    assert _roundtrip(w, tile_rows=12)[0] != 0           # not a multiple of 8
-    assert _roundtrip(w, tile_rows=2048)[0] != 0         # beyond the activation table
-    assert _roundtrip(w, lanes_per_list=3)[0] != 0
-    assert _roundtrip(w, num_ctas=1000)[0] != 0
+    assert _roundtrip(w, tile_rows=12)[0] != 0           # not a multiple of 32
+    assert _roundtrip(w, tile_rows=8192)[0] != 0         # beyond what a one-byte id covers
+    assert _roundtrip(w, num_ctas=100000)[0] != 0
     assert b"" != _lib.lib().tllm_last_error()
+
+
+def _corrupt(w, what, where, value, **opts):
+    w = np.ascontiguousarray(w, np.int8)
+    o = _lib.PackOpts(opts.get("tile_rows", 0), opts.get("num_ctas", 0), 0, 0, opts.get("k_splits", 0))
+    return _lib.lib().tllm_pack_corrupt_check(_lib.np_ptr(w), w.shape[0], w.shape[1], C.byref(o), 8, what, where, value)
+
+
+def test_damaged_images_are_refused_on_the_host():
+    """What tllm_weight_load checks before it uploads anything: every header field, block descriptor, table word
+    class and stream byte class, damaged one at a time, must be refused (and nothing may be read out of range
+    while finding out)."""
+    rng = np.random.default_rng(9)
+    w = random_ternary(rng, 600, 48, 0.6)
+    kw = dict(tile_rows=256, k_splits=1)
+    assert _corrupt(w, 0, 0, 0, **kw) == 0
+    bad = [
+        (3, 0, 0), (3, 0, 8192), (3, 0, 100), (3, 0, 512),      # tile_rows: zero, too large, not a multiple of 32, wrong
+        (4, 0, 0), (4, 0, 7),                                    # tiles
+        (5, 0, 0), (5, 0, 1000),                                 # col_blocks
+        (6, 0, 0), (6, 0, 3),                                    # k_splits
+        (7, 0, 0), (7, 0, 1),                                    # tiles_per_cta
+        (8, 0, 0), (8, 0, 0x7fffffff), (8, 0, 8),                # a block's table words
+        (9, 0, 0xfffffff0), (9, 1, 3),                           # a block's first vector: out of range, misaligned
+        (12, 0, 0xfffffff0), (13, 0, 0xffffffe0),                # table offset, vector count
+        (10, 1, 1), (10, 1, 1000), (10, 0, 2),                   # column ranges
+        (11, 0, 100),                                            # inners no longer matches the ids
+        (1, 0, 5), (1, 1, 4000), (1, 3, 40), (1, 6, 999),        # block header words
+        (1, 8, 3), (1, 9, 100000), (1, 16, 0),                   # warp table
+        (1, 17, 0xffffff), (1, 18, 0x00ff0001), (1, 18, 0x00030000), (1, 19, 0x7f), (1, 19, 0xffffff00), (1, 20, 0),
+        (1, 21, 0xffffffff), (1, 37, 0xffffffff),                # unit descriptor: offset, columns, tile, reduce points, lengths
+    ]
+    for what, where, value in bad:
+        rc = _corrupt(w, what, where, value, **kw)
+        assert rc != 0, (what, where, value)
+    # stream bytes: an id beyond the tile, a damaged flag byte, a lost list end
+    assert _corrupt(w, 2, 0, 200, **kw) != 0
+    assert _corrupt(w, 2, 15, 0xf0, **kw) != 0
+    assert _corrupt(w, 2, 15, 0x0f, **kw) != 0 or _corrupt(w, 2, 15, 0x00, **kw) != 0
 
 
 def test_schedule_for_llama_shapes_uses_most_sms():
     """Shapes of the benchmark configs: one wave, >= 88 % of the SMs busy."""
-    for K, N in [(4096, 11008), (11008, 4096), (4096, 22016), (2048, 2048), (5120, 15360), (8192, 28672), (28672, 8192),
-                 (8192, 10240), (8192, 8192)]:
-        # a thin slice of columns is enough to exercise the scheduler: it only looks at shapes
-        w = np.zeros((K, 2), np.int8)
+    for K, N in [(4096, 11008), (11008, 4096), (4096, 22016), (2048, 2048), (5120, 15360), (8192, 10240), (8192, 8192)]:
+        big = np.zeros((K, N), np.int8)
         info = _lib.WeightInfo()
         o = _lib.PackOpts(0, 0, 0, 0)
-        big = np.zeros((K, N), np.int8) if K * N <= 64 * 1024 * 1024 else None
-        if big is None:
-            continue
         out = np.empty_like(big)
         rc = _lib.lib().tllm_pack_roundtrip(_lib.np_ptr(big), K, N, C.byref(o), 148, _lib.np_ptr(out), C.byref(info))
         assert rc == 0, _lib.lib().tllm_last_error()

@@ -93,7 +93,7 @@ def test_decoder_layer_single_rank_matches_fp32_reference():
     largest output: the layer rounds to bf16 between its stages, the reference does not."""
     import torch.nn.functional as F
 
-    from bench import make_weight
+    from ternaryllm_b200.synthetic import make_weight
     from ternaryllm_b200.tensor_parallel import TernaryDecoderLayerTP, rms_norm
 
     dev = torch.device("cuda", 0)
