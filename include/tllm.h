@@ -261,6 +261,37 @@ int tllm_silu_mul(void* g, const void* u, int dtype, int64_t n, void* stream);
 int tllm_add_rmsnorm(void* x, const void* delta, const void* weight, void* h, int dtype, int rows, int hidden,
                      float eps, void* stream);
 
+/* --------------------------------------------------------------------------------------------------
+ * Tensor-parallel glue: the all-reduce that follows a row-sharded product (O and down projections), fused with
+ * the residual add and RMSNorm that follow it, in one kernel per GPU over peer-mapped memory.  The reference has
+ * no distributed code; the partitioning is the usual one (column-sharded QKV / gate / up, row-sharded O / down).
+ *
+ *   x[r] += sum over ranks of partial_rank[r]        (fp32 partial sums, added in rank order on every GPU: all
+ *   h[r]  = x[r] * rsqrt(mean(x[r]^2) + eps) * w      ranks compute identical bits; x rounded once to its type)
+ *
+ * One process per GPU.  Every rank creates a communicator (receive slots for max_rows x hidden partial sums from
+ * each rank, double-buffered, plus flags), exports two inter-process memory handles (tllm_comm_handle_bytes bytes),
+ * the caller all-gathers them with whatever it uses for rendezvous (torch.distributed in this package) and every
+ * rank connects.  Each call pushes the rank's rows into its slot on every peer with plain stores over NVLink,
+ * releases a flag per peer, waits (bounded: tllm_comm_set_wait_limit, default about a second) for the peers' flags
+ * and reduces.  All ranks must make the same sequence of calls with the same row counts.  A wait that runs out
+ * leaves the result undefined and is reported by tllm_comm_check, after which the communicator must be destroyed
+ * on every rank.  No cluster-multicast loads and no library kernels touch peer memory.
+ * tllm_comm_attach wires a peer to buffers the caller names (tests on one GPU: a stand-in peer whose slot and flag
+ * the host fills). */
+typedef struct tllm_comm tllm_comm;
+int tllm_comm_create(int world, int rank, int max_rows, int hidden, tllm_comm** out);
+int tllm_comm_handle_bytes(void);
+int tllm_comm_export(tllm_comm* c, void* handle);
+int tllm_comm_connect(tllm_comm* c, const void* handles /* world * tllm_comm_handle_bytes(), in rank order */);
+int tllm_comm_attach(tllm_comm* c, int peer, void* recv, void* flags);
+int tllm_comm_buffers(tllm_comm* c, void** recv, void** flags, int64_t* recv_bytes, int64_t* flag_bytes);
+int tllm_comm_set_wait_limit(tllm_comm* c, double milliseconds);
+int tllm_comm_check(tllm_comm* c);
+int tllm_comm_destroy(tllm_comm* c);
+int tllm_allreduce_add_rmsnorm(tllm_comm* c, const float* partial, void* x, const void* weight, void* h, int dtype,
+                               int rows, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

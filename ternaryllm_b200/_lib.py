@@ -69,6 +69,16 @@ SIGNATURES = {
     "tllm_mlp_get_info": (_I, [_P, _P, _P]),
     "tllm_silu_mul": (_I, [_P, _P, _I, _L, _P]),
     "tllm_add_rmsnorm": (_I, [_P, _P, _P, _P, _I, _I, _I, _F, _P]),
+    "tllm_comm_create": (_I, [_I, _I, _I, _I, _P]),
+    "tllm_comm_handle_bytes": (_I, []),
+    "tllm_comm_export": (_I, [_P, _P]),
+    "tllm_comm_connect": (_I, [_P, _P]),
+    "tllm_comm_attach": (_I, [_P, _I, _P, _P]),
+    "tllm_comm_buffers": (_I, [_P, _P, _P, _P, _P]),
+    "tllm_comm_set_wait_limit": (_I, [_P, C.c_double]),
+    "tllm_comm_check": (_I, [_P]),
+    "tllm_comm_destroy": (_I, [_P]),
+    "tllm_allreduce_add_rmsnorm": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _P]),
 }
 
 _lib = None

@@ -154,8 +154,7 @@ const char* bs_pack_dense(const int8_t* w, int inners, int columns, const tllm_p
     if ((int64_t)inners * columns > ((int64_t)1 << 40)) return "pack: matrix too large";
     tllm_pack_opts o{};
     if (opts) o = *opts;
-    int ctas = o.num_ctas > 0 ? o.num_ctas : num_sms;
-    if (ctas <= 0 || ctas > BS_MAX_BLOCKS) return "pack: num_ctas out of range";
+    if (o.num_ctas < 0 || o.num_ctas > BS_MAX_BLOCKS || num_sms <= 0 || num_sms > BS_MAX_BLOCKS / 4) return "pack: num_ctas out of range";
     int T = o.tile_rows > 0 ? o.tile_rows : BS_TILE_ROWS;
     if (T > BS_TILE_ROWS || T % 32) return "pack: tile_rows must be a multiple of 32 and at most 4096";
     const int tiles = (inners + T - 1) / T;
@@ -169,6 +168,16 @@ const char* bs_pack_dense(const int8_t* w, int inners, int columns, const tllm_p
     L.tile_rows = T;
     L.tiles = tiles;
     L.nnz = (int64_t)cl.pos_row.size() + (int64_t)cl.neg_row.size();
+
+    // Blocks per SM: a block is eight warps, and the walk is bound by instruction issue and latency, not by bytes, so an
+    // SM wants 16 warps of a small product (two more blocks of the next product in the stream wait beside them with
+    // their tables and first index vectors already fetched) and 32 warps of a large one.
+    int ctas = o.num_ctas;
+    if (ctas <= 0) {
+        int per_sm = L.nnz / num_sms > 300000 ? 4 : 2;
+        while (per_sm > 1 && columns / (per_sm * num_sms) < 16) per_sm /= 2;
+        ctas = per_sm * num_sms;
+    }
 
     // K-splits: blocks share a column range along K only where the columns alone would leave a warp with less than
     // four columns of a tile (short units waste lanes at their ragged ends); then every block takes one tile

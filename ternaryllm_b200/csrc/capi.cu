@@ -30,6 +30,8 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 #define CU_TRY(expr)                                                                                       \
     do {                                                                                                   \
         cudaError_t e_ = (expr);                                                                           \
@@ -134,7 +136,7 @@ struct Scratch {
 
 template <typename ACC, int MP>
 int launch_bs(const BsParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = bstream_spmm_kernel<ACC, MP, 4, 3>;
+    auto kern = bstream_spmm_kernel<ACC, MP>;
     static std::mutex mu;
     static bool configured[64] = {};
     int dev = 0;
@@ -290,9 +292,13 @@ int run_mm(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void*
     return TLLM_OK;
 }
 
-// K-tiles whose activation tables one launch keeps in shared memory: 64.5 KiB of tables at most
+// K-tiles whose activation tables one launch keeps in shared memory at the same time (the rest follow, one barrier-
+// separated group after the other): small tables leave room for four blocks per SM
+#ifndef BS_RESIDENT_MAX
+#define BS_RESIDENT_MAX 2
+#endif
 int resident_tiles(int mp, int tiles_per_cta) {
-    const int fit = 4 / mp;
+    const int fit = BS_RESIDENT_MAX / mp > 0 ? BS_RESIDENT_MAX / mp : 1;
     return tiles_per_cta < fit ? tiles_per_cta : fit;
 }
 
@@ -329,8 +335,8 @@ int run_bs(tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, i
     p.l2_prefetch_bytes = 256u * 1024u;
     p.scale = scale;
     p.scale2 = scale2;
-    const BsSmem sm = bs_smem_layout(mp, p.resident, L.tiles_per_cta, L.max_cols_per_block, w->max_meta_words);
-    p.off_table = sm.off_table, p.off_cells = sm.off_cells, p.off_meta = sm.off_meta, p.off_bars = sm.off_bars;
+    const BsSmem sm = bs_smem_layout(mp, p.resident, L.tiles_per_cta, L.max_cols_per_block, w->max_meta_words, BS_STAGE_BYTES);
+    p.off_table = sm.off_table, p.off_cells = sm.off_cells, p.off_meta = sm.off_meta, p.off_bars = sm.off_bars, p.off_stage = sm.off_stage;
     if (sm.total > 227u * 1024u) return fail(TLLM_ERR_ARG, "gather kernel: this weight needs %u bytes of shared memory per block", sm.total);
     p.cta_ext = w->d_cta;
     std::memcpy(p.cta, L.cta.data(), sizeof(TsCtaDesc) * (size_t)(L.num_ctas < BS_MAX_PARAM_BLOCKS ? L.num_ctas : BS_MAX_PARAM_BLOCKS));
@@ -480,6 +486,13 @@ void bs_fill_info(const BsLayout& L, tllm_weight_info* info) {
     info->algorithmic_bytes = 2 * L.nnz + 16 * (int64_t)L.columns * ((L.inners + 511) / 512);
 }
 }  // namespace tllm
+
+#ifdef BS_TRACE
+extern "C" int tllm_debug_set_trace(void* device_buffer) {
+    CU_TRY(cudaMemcpyToSymbol(tllm::g_bs_trace, &device_buffer, sizeof(void*)));
+    return TLLM_OK;
+}
+#endif
 
 extern "C" {
 

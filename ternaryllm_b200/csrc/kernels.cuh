@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(256) mcsc_spmm_kernel(const void* __restrict__
 }
 
 // g[i] = silu(g[i]) * u[i]
-__global__ void silu_mul_kernel(void* g, const void* u, int dtype, long long n) {
+static __global__ void silu_mul_kernel(void* g, const void* u, int dtype, long long n) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float a = load_act_f32(g, dtype, (size_t)i), bq = load_act_f32(u, dtype, (size_t)i);
@@ -198,7 +198,7 @@ __global__ void silu_mul_kernel(void* g, const void* u, int dtype, long long n) 
 }
 
 // y[i] += bias[i % columns], both of `dtype` (fp32 sum, rounded once; int32 adds exactly)
-__global__ void bias_add_kernel(void* y, const void* bias, int dtype, long long n, int columns) {
+static __global__ void bias_add_kernel(void* y, const void* bias, int dtype, long long n, int columns) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int c = (int)(i % columns);

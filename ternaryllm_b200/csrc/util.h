@@ -8,6 +8,9 @@ namespace tllm {
 // Records a printf-style message for the calling thread (returned by tllm_last_error) and returns `code`.
 int fail(int code, const char* fmt, ...);
 
+// counts one kernel launch (tllm_launch_count)
+void note_launch();
+
 // decoders of the reference's formats into dense int8 [inners][columns]; return nullptr or a message
 const char* decode_mcsc(const int32_t* row_idx, const int32_t* off, int columns, int inners, int tile_k,
                         std::vector<int8_t>* out);

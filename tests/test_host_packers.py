@@ -97,7 +97,7 @@ def test_bank_stream_roundtrip(K, N, s):
     assert rc == 0, _lib.lib().tllm_last_error()
     assert np.array_equal(out, w)
     assert info["nnz"] == int((w != 0).sum())
-    assert info["num_ctas"] <= 148 and info["num_ctas"] == info["col_blocks"] * info["k_splits"]
+    assert info["num_ctas"] <= 2 * 148 and info["num_ctas"] == info["col_blocks"] * info["k_splits"]
     assert info["tiles"] == -(-K // 4096)
 
 
@@ -113,11 +113,11 @@ def test_bank_stream_storage_at_benchmark_density():
     w[r >= 224] = 1
     rc, out, info = _roundtrip(w, num_sms=37)
     assert rc == 0 and np.array_equal(out, w)
-    assert info["k_splits"] == 1 and info["num_ctas"] == 37 and info["tiles"] == 1
+    assert info["k_splits"] == 1 and info["num_ctas"] == 74 and info["tiles"] == 1      # two blocks per SM
     assert info["stream_bytes"] + info["meta_bytes"] <= 0.6 * info["algorithmic_bytes"], info
     assert info["meta_bytes"] <= 0.02 * info["stream_bytes"]
     # every warp of every block got one unit: the lanes never drift more than a ring apart on random data
-    assert info["units"] == 37 * 8
+    assert info["units"] == 74 * 8
 
 
 def test_bank_stream_edge_cases():
@@ -207,7 +207,7 @@ def test_schedule_for_llama_shapes_uses_most_sms():
         out = np.empty_like(big)
         rc = _lib.lib().tllm_pack_roundtrip(_lib.np_ptr(big), K, N, C.byref(o), 148, _lib.np_ptr(out), C.byref(info))
         assert rc == 0, _lib.lib().tllm_last_error()
-        assert info.num_ctas <= 148 and info.num_ctas >= 130, (K, N, info.as_dict())
+        assert info.num_ctas <= 4 * 148 and info.num_ctas >= 130, (K, N, info.as_dict())
 
 
 def test_cpu_format_decoders_build_the_same_dense_matrix(cpu_reference):
