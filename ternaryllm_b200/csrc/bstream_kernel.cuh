@@ -259,12 +259,12 @@ __device__ __noinline__ void bs_reduce_batch(const BsParams& p, uint32_t ring, u
 #define BS_AHEAD 3          // < BS_DEPTH: the slot being read is never the one being refilled
 #endif
 #ifndef BS_MIN_BLOCKS
-#define BS_MIN_BLOCKS 4
-#endif
+#define BS_MIN_BLOCKS 4     // blocks per SM the one-row kernel's registers leave room for (two and four rows: 2 and 1,
+#endif                      // their shared memory allows no more)
 #define BS_STAGE_BYTES ((uint32_t)BS_WARPS * BS_DEPTH * 512u)
 
 template <typename ACC, int MP>
-__global__ void __launch_bounds__(BS_WARPS * 32, BS_MIN_BLOCKS) bstream_spmm_kernel(const __grid_constant__ BsParams p) {
+__global__ void __launch_bounds__(BS_WARPS * 32, MP == 1 ? BS_MIN_BLOCKS : (MP == 2 ? 2 : 1)) bstream_spmm_kernel(const __grid_constant__ BsParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr uint32_t EB = 4u * MP;                        // bytes of one table entry / lane cell
     constexpr uint32_t ROWB = 128u * MP;                    // one row group of the table, one slot of a ring
@@ -385,9 +385,45 @@ __global__ void __launch_bounds__(BS_WARPS * 32, BS_MIN_BLOCKS) bstream_spmm_ker
                 ACC a, b, c, d;
             };
             const int nchunks = fill / KPC;
+            // Several activation rows that 128-bit loads can reach: the raw rows are first copied into the (still unused)
+            // ring area, row m at m * rows_here elements, with every load of a thread issued before its first store; the
+            // table entries are then put together from shared memory.
+            const bool staged = MP > 1 && p.x_vec;
+            if (staged) {
+                if (r > 0) __syncthreads();   // the previous tile's raw rows have been consumed
+                const uint32_t eb = act_bytes(p.x_dtype);
+                const int vec_per_row = rows_here * (int)eb / 16, total = p.M * vec_per_row;
+                for (int v0 = tid; v0 < total; v0 += NT * UF) {
+                    uint4 raw[UF];
+#pragma unroll
+                    for (int u = 0; u < UF; ++u) {
+                        const int vi = v0 + u * NT;
+                        if (vi < total) {
+                            const int m = vi / vec_per_row, o = vi - m * vec_per_row;
+                            raw[u] = __ldcg((const uint4*)((const char*)p.X + ((size_t)m * p.x_ld + kbase) * eb) + o);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < UF; ++u) {
+                        const int vi = v0 + u * NT;
+                        if (vi < total) *(uint4*)(sm + (size_t)vi * 16u) = raw[u];
+                    }
+                }
+                __syncthreads();
+            }
             for (int c0f = tid; c0f < nchunks; c0f += NT * UF) {
                 ACC v[UF][4];
-                if (MP == 1 && p.x_vec) {
+                if (staged) {
+#pragma unroll
+                    for (int u = 0; u < UF; ++u) {
+                        const int k = (c0f + u * NT) * KPC;
+#pragma unroll
+                        for (int kk = 0; kk < KPC; ++kk)
+#pragma unroll
+                            for (int m = 0; m < MP; ++m)
+                                v[u][kk * MP + m] = (m < p.M && k + kk < rows_here) ? staged_act<ACC>(sm, p.x_dtype, (uint32_t)(m * rows_here + k + kk)) : (ACC)0;
+                    }
+                } else if (MP == 1 && p.x_vec) {
                     // four consecutive activations of the one row per load (rows_here is a multiple of 16 here)
                     const uint32_t eb = act_bytes(p.x_dtype);
                     uint4 raw[UF];

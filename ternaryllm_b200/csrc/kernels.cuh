@@ -133,6 +133,21 @@ __device__ __forceinline__ float load_act_cg<float>(const void* X, int dtype, si
 template <>
 __device__ __forceinline__ int load_act_cg<int>(const void* X, int dtype, size_t i) { return load_act_i32_cg(X, dtype, i); }
 
+// activation element i of a raw tile staged in shared memory
+template <typename ACC>
+__device__ __forceinline__ ACC staged_act(const unsigned char* st, int dtype, uint32_t i);
+template <>
+__device__ __forceinline__ float staged_act<float>(const unsigned char* st, int dtype, uint32_t i) {
+    switch (dtype) {
+        case TLLM_F32: return ((const float*)st)[i];
+        case TLLM_F16: return __half2float(((const __half*)st)[i]);
+        case TLLM_BF16: return __bfloat162float(((const __nv_bfloat16*)st)[i]);
+        default: return (float)((const signed char*)st)[i];
+    }
+}
+template <>
+__device__ __forceinline__ int staged_act<int>(const unsigned char* st, int dtype, uint32_t i) { return (int)((const signed char*)st)[i]; }
+
 __device__ __forceinline__ uint32_t act_bytes(int dtype) { return dtype == TLLM_F32 ? 4u : (dtype == TLLM_I8 ? 1u : 2u); }
 
 // ---------------------------------------------------------------------------------------------------
