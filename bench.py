@@ -1,20 +1,29 @@
 #!/usr/bin/env python
 """Benchmark of the ternary sparse product hot path on B200.
 
-Workload (the configuration the headline metric is quoted on): decode ternary SpMV, Llama-7B
-up-projection shape -- x [M=1, 4096] fp16 ~ N(0,1), W [4096, 11008] ternary with 75 % zeros and +-1
-equiprobable, per-tensor fp16 scale ~ U(0.01, 0.05), seeded synthetic data.
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 bench.py --gpus N ...
 
-One step = one decode token pushed through R distinct packed weights of that shape (R*bytes is several
-times the L2 capacity, so every launch streams its weight from HBM).  `value` is algorithmic GB/s
-(B_alg per launch / average launch time): B_alg = 2*nnz + 16*N*ceil(K/512) + e*M*(K+N) + 4 bytes, the
-bytes of the reference's own layout.  `e2e` is the same metric through the host-buffer C-ABI entry point
-(tllm_spmm_host): pinned host x -> device, kernel, y -> host, every call.
+One JSON line on rank 0.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--rows M] [--sparsity S]
+Headline (`metric`, `value`): decode tokens/s of the tensor-parallel ternary Llama-70B-shaped decoder stack
+(hidden 8192, FFN 28672, 64 query / 8 KV heads of 128, 80 layers, 50 % zeros, bf16 activations, KV length 1024) at
+decode batch 1, on N GPUs of one node -- strong scaling: the same model at every N.  Every rank packs its shards of
+the same seeded weights; before anything is timed, one layer's output on the N ranks is compared with the same
+layer computed with dense fp32 matrices on rank 0.  A step is one token through all layers, replayed from a CUDA
+graph; batches 16 and 64, the other sparsities and a per-layer breakdown are reported beside the headline.
 
-With --impl reference the reference's own CPU GEMV kernels (compiled in place into oracle/_ref) are timed
-on the host cores for the same workload; that arm launches no GPU kernel.
+`roofline` is that of the kernel that dominates the step, the decode product on one activation row, measured in
+the same run on its own headline workload: x [1, 4096] fp16 ~ N(0,1), W [4096, 11008] ternary with 75 % zeros, fp16
+scale ~ U(0.01, 0.05), R distinct packed weights replayed back to back from a CUDA graph (R weights exceed the L2
+capacity several times).  achieved = B_alg / average launch time, B_alg = 2*nnz + 16*N*ceil(K/512) + e*M*(K+N) + 4
+bytes (the reference layout's bytes); `spmv` carries the same for 50..90 % zeros and the neighbouring configurations.
+
+`e2e` is the headline metric through host buffers: the token's activations start in pinned host memory and the
+step's result is read back to the host, every step.
+
+With --impl reference the reference's own CPU kernels (compiled in place into oracle/_ref) are timed on the host
+cores on a bounded sample of the same step (one layer's linears, scaled to the layer count); no GPU kernel runs.
 """
 from __future__ import annotations
 
@@ -31,14 +40,15 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from ternaryllm_b200.synthetic import make_weight  # noqa: E402
+from ternaryllm_b200.synthetic import block_weight, make_weight  # noqa: E402
 
 K_IN, N_OUT = 4096, 11008
 L2_BYTES = 126 * 1024 * 1024
-METRIC = "ternary_spmv_algorithmic_hbm_gbps"
-# DRAM bytes per launch of the decode kernel from an ncu capture of this workload at one row
-# (dram__bytes_read.sum + dram__bytes_write.sum = 23.70 MB + 0; profiles/tstream_spmm_decode_4096x11008_s75_m1.md).
-NCU_TRAFFIC_BYTES = 23.70e6
+METRIC = "ternary_llama70b_shape_decode_tokens_per_s"
+DEC = dict(hidden=8192, ffn=28672, heads=64, kv_heads=8, head_dim=128, layers=80, kv_len=1024)
+# DRAM bytes per launch of the decode kernel from an ncu capture of the headline product (dram__bytes_read.sum +
+# dram__bytes_write.sum); refreshed whenever the kernel or the format changes
+NCU_TRAFFIC = {"bytes": 13.58e6, "source": "ncu, profiles/bstream_spmm_decode_4096x11008_s75_m1.md"}
 
 
 def algorithmic_bytes(nnz: int, K: int, N: int, M: int, e: int) -> int:
@@ -111,298 +121,186 @@ def measured_peak(key="hbm_gbs", fallback=6650.0):
     return fallback, "fallback"
 
 
-def graph_time_us(torch, fn, reps, warmup=3):
-    """Average time of fn() in microseconds over `reps` replays of a CUDA graph of one call (plain launches if the
-    capture fails), CUDA events on the current stream."""
-    fn()
+def capture(torch, fn):
+    """fn() captured into a CUDA graph (after one eager run on a side stream); returns the graph."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
-    run = fn
-    try:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            fn()
-        torch.cuda.current_stream().wait_stream(side)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            fn()
-        run = g.replay
-    except Exception:
-        torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, capture_error_mode="thread_local"):
+        fn()
+    return g
+
+
+def timed_us(torch, run, min_seconds=0.2, warmup=3, max_reps=200000):
+    """Average time of run() in microseconds: CUDA events on the current stream around enough back-to-back calls to
+    fill `min_seconds`."""
     for _ in range(warmup):
         run()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    run()
+    e1.record()
+    torch.cuda.synchronize()
+    one = max(e0.elapsed_time(e1) * 1e-3, 1e-6)
+    reps = int(min(max_reps, max(3, min_seconds / one)))
+    e0.record()
     for _ in range(reps):
         run()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) * 1e3 / reps
+    return e0.elapsed_time(e1) * 1e3 / reps, reps
 
 
-def other_configs(torch, device, packed, nnz, K, N, peak_hbm):
-    """Short measurements of the neighbouring configurations (each a few hundred replays): the same weights at
-    4 and 16 rows, the fused MLP block of the same shape at 60 % zeros, and the 13B-shape QKV prefill product on
-    the tensor cores.  Reported beside the headline, not part of it."""
+# ------------------------------------------------------------------------------------------------------
+# the decode product on its own workloads (roofline of the dominant kernel, sparsity sweep, neighbours)
+# ------------------------------------------------------------------------------------------------------
+def spmv_records(torch, device, peak_hbm, quick=False):
     from ternaryllm_b200 import PackedMLP, PackedWeight, _lib
 
     L = _lib.lib()
-    out = []
-    R = len(packed)
-    for M in (4, 16):
-        X = torch.randn((M, K), device=device).to(torch.float16)
-        Y = torch.empty((M, N), dtype=torch.float16, device=device)
-        n0, m0 = L.tllm_launch_count(), L.tllm_mma_launch_count()
+    rng = np.random.default_rng(12345)
+    out = {"sweep": [], "other_configs": []}
 
-        def fn():
-            for w in packed:
-                w.matmul(X, out=Y)
+    def product(K, N, S, M, dtype=torch.float16, seed0=1000, check=True):
+        """R distinct weights of one shape replayed from a graph; returns a record"""
+        e = torch.empty((), dtype=dtype).element_size()
+        bytes_one = int(K * N * (1 - S)) * 1.1 + 1
+        R = min(48, max(3, int(-(-3 * L2_BYTES // bytes_one)) + 1))     # small weights stay (and are marked) L2-resident
+        scales = [float(np.float16(v)) for v in rng.uniform(0.01, 0.05, R)]
+        packed, nnzs, w0 = [], [], None
+        for i in range(R):
+            w = make_weight(seed0 + i, K, N, S)
+            nnzs.append(int((w != 0).sum()))
+            packed.append(PackedWeight.from_dense(w, scale=scales[i], device=device))
+            if i == 0:
+                w0 = w
+        nnz = int(np.mean(nnzs))
+        info = packed[0].info
+        X = torch.tensor(rng.standard_normal((M, K)), dtype=dtype, device=device)
+        Y = [torch.empty((M, N), dtype=dtype, device=device) for _ in range(R)]
+        m0 = L.tllm_mma_launch_count()
 
-        us = graph_time_us(torch, fn, 50) / R
+        def step():
+            for i in range(R):
+                packed[i].matmul(X, out=Y[i])
+
+        step()
+        torch.cuda.synchronize()
         tensor = L.tllm_mma_launch_count() > m0
-        balg = algorithmic_bytes(nnz, K, N, M, 2)
-        out.append({"workload": f"same weights, {M} rows fp16", "kernel": "tensor-core" if tensor else "gather", "us_per_launch": us,
-                    "algorithmic_GBps": balg / us / 1e3, "frac_of_hbm_peak": balg / us / 1e3 / peak_hbm,
-                    "GOPs": M * nnz / us / 1e3})
-    # fused MLP 4096 -> 11008 -> 4096, 60 % zeros, fp16
+        err = None
+        if check:
+            ref = (X.double() @ torch.tensor(w0, device=device).double()) * scales[0]
+            err = float((Y[0].double() - ref).abs().max() / ref.abs().max())
+            if not err <= 1e-3 + 2.0 ** -8:
+                raise SystemExit(f"benchmark output differs from the dense product (rel err {err}) at {K}x{N} S={S} M={M}")
+        g = capture(torch, step)
+        us, reps = timed_us(torch, g.replay, 0.05 if quick else 0.2)
+        us /= R
+        for p in packed:
+            p.check()
+        balg = algorithmic_bytes(nnz, K, N, M, e)
+        bphys = (info["bit_tile_bytes"] if tensor else info["stream_bytes"] + info["meta_bytes"]) + e * M * (K + N)
+        rec = {"K": K, "N": N, "zeros": S, "rows": M, "kernel": "tensor-core" if tensor else "gather", "us_per_launch": us,
+               "algorithmic_GBps": balg / us / 1e3, "frac": balg / us / 1e3 / peak_hbm, "physical_bytes": int(bphys),
+               "frac_physical": bphys / us / 1e3 / peak_hbm, "GOPs": M * nnz / us / 1e3, "weights_in_rotation": R, "rotation_exceeds_l2": bool(R * bytes_one > 2 * L2_BYTES),
+               "graph_replays_timed": reps, "check_rel_err": err, "algorithmic_bytes": balg, "nnz": nnz,
+               "pack": {k: info[k] for k in ("tile_rows", "tiles", "col_blocks", "k_splits", "num_ctas", "units")}}
+        for p in packed:
+            p.close()
+        return rec
+
+    out["headline"] = product(K_IN, N_OUT, 0.75, 1)
+    for S in ((0.5, 0.9) if quick else (0.5, 0.6, 0.7, 0.8, 0.9)):
+        out["sweep"].append(product(K_IN, N_OUT, S, 1, seed0=2000 + int(S * 100)))
+    if quick:
+        return out
+    for M in (4, 16):
+        out["other_configs"].append(dict(product(K_IN, N_OUT, 0.75, M, seed0=1000), workload=f"C2 up-projection shape, {M} rows fp16"))
+    out["other_configs"].append(dict(product(8192, 28672, 0.5, 1, dtype=torch.bfloat16, seed0=3000), workload="70B up-projection shape, 1 row bf16"))
+    # C1: the reference's own CPU case, M = 8, K = N = 2048, fp32 N(0,1), 50 % zeros
+    out["other_configs"].append(dict(product(2048, 2048, 0.5, 8, dtype=torch.float32, seed0=0), workload="C1: X[8,2048] fp32, W[2048,2048] 50% zeros"))
+    # C3: fused MLP 4096 -> 11008 -> 4096, 60 % zeros, fp16 (two launches per block: gate|up with SiLU*mul, then down)
+    import oracle
+
     hidden, inter, S = 4096, 11008, 0.6
-    mlps, rng = [], np.random.default_rng(777)
+    mlps, mrng = [], np.random.default_rng(777)
+    wsets = []
     for i in range(3):
-        sg, su, sd = (float(np.float16(v)) for v in rng.uniform(0.01, 0.05, 3))
-        mlps.append(PackedMLP(make_weight(50 + 3 * i, hidden, inter, S), make_weight(51 + 3 * i, hidden, inter, S),
-                              make_weight(52 + 3 * i, inter, hidden, S), sg, su, sd, device))
-    infos = mlps[0].info
-    balg_w = sum(i["algorithmic_bytes"] for i in infos)
+        sg, su, sd = (float(np.float16(v)) for v in mrng.uniform(0.01, 0.05, 3))
+        ws = (make_weight(50 + 3 * i, hidden, inter, S), make_weight(51 + 3 * i, hidden, inter, S), make_weight(52 + 3 * i, inter, hidden, S))
+        mlps.append(PackedMLP(*ws, sg, su, sd, device))
+        wsets.append((ws, (sg, su, sd)))
+    balg_w = sum(i["algorithmic_bytes"] for i in mlps[0].info)
     for M in (1, 8, 32):
-        X = torch.randn((M, hidden), device=device).to(torch.float16)
+        X = torch.tensor(mrng.standard_normal((M, hidden)), dtype=torch.float16, device=device)
         Y = torch.empty((M, hidden), dtype=torch.float16, device=device)
         H = torch.empty((M, inter), dtype=torch.float16, device=device)
         m0 = L.tllm_mma_launch_count()
+        mlps[0].forward(X, out=Y, h=H)
+        torch.cuda.synchronize()
+        (wg, wu, wd), (sg, su, sd) = wsets[0]
+        rows = min(M, 2)          # the fp64 oracle on two rows of the full-size block
+        ref = oracle.mlp_f64(X[:rows].double().cpu().numpy(), wg, wu, wd, sg, su, sd, h_round=1)
+        err = float(np.max(np.abs(Y[:rows].double().cpu().numpy() - ref)) / np.max(np.abs(ref)))
+        if not err <= 1e-3 + 2.0 ** -9:
+            raise SystemExit(f"fused MLP differs from the oracle (rel err {err}) at {M} rows")
 
         def fn():
             for m in mlps:
                 m.forward(X, out=Y, h=H)
 
-        us = graph_time_us(torch, fn, 50) / len(mlps)
+        g = capture(torch, fn)
+        us, _ = timed_us(torch, g.replay, 0.1)
+        us /= len(mlps)
         balg = balg_w + 2 * M * 2 * hidden
-        out.append({"workload": f"fused MLP block {hidden}->{inter}->{hidden}, 60% zeros, {M} rows fp16 (two launches)",
-                    "kernel": "tensor-core" if L.tllm_mma_launch_count() > m0 else "gather", "us_per_block": us,
-                    "algorithmic_GBps": balg / us / 1e3, "frac_of_hbm_peak": balg / us / 1e3 / peak_hbm})
+        out["other_configs"].append({"workload": f"C3: MLP block {hidden}->{inter}->{hidden}, 60% zeros, {M} rows fp16 (two launches)",
+                                     "kernel": "tensor-core" if L.tllm_mma_launch_count() > m0 else "gather", "us_per_block": us,
+                                     "algorithmic_GBps": balg / us / 1e3, "frac": balg / us / 1e3 / peak_hbm, "check_rel_err": err})
     for m in mlps:
         m.close()
-    # attention-projection prefill, 13B shape: X [2048, 5120] bf16, W [5120, 15360] at 50 % zeros
-    Kp, Np, Mp = 5120, 15360, 2048
-    wq = PackedWeight.from_dense(make_weight(90, Kp, Np, 0.5), scale=0.02, device=device)
-    X = torch.randn((Mp, Kp), device=device).to(torch.bfloat16)
-    Y = torch.empty((Mp, Np), dtype=torch.bfloat16, device=device)
-    m0 = L.tllm_mma_launch_count()
-    us = graph_time_us(torch, lambda: wq.matmul(X, out=Y), 20)
+    # C4: attention projections, 13B shape prefill, X [2048, 5120] bf16 against W [5120, 15360] and W [5120, 5120], 50 % zeros
     peak_tc, kind = measured_peak("bf16_tflops", 1590.0)
-    tf = 2.0 * Mp * Kp * Np / us / 1e6
-    out.append({"workload": f"QKV prefill, X[{Mp},{Kp}] bf16, W[{Kp},{Np}] 50% zeros", "kernel": "tensor-core" if L.tllm_mma_launch_count() > m0 else "gather",
-                "us_per_launch": us, "dense_equivalent_TFLOPs": tf, "frac_of_bf16_peak": tf / peak_tc, "bf16_peak_TFLOPs": peak_tc, "peak_source": kind})
-    wq.close()
+    for Np, name in ((15360, "QKV"), (5120, "O")):
+        Kp, Mp = 5120, 2048
+        w = make_weight(90 + Np, Kp, Np, 0.5)
+        wq = PackedWeight.from_dense(w, scale=0.02, device=device)
+        X = torch.randn((Mp, Kp), device=device).to(torch.bfloat16)
+        Y = torch.empty((Mp, Np), dtype=torch.bfloat16, device=device)
+        m0 = L.tllm_mma_launch_count()
+        wq.matmul(X, out=Y)
+        ref = (X[:128].double() @ torch.tensor(w, device=device).double()) * 0.02
+        err = float((Y[:128].double() - ref).abs().max() / ref.abs().max())
+        if not err <= 1e-3 + 2.0 ** -8:
+            raise SystemExit(f"prefill product differs from the dense product (rel err {err})")
+        us, _ = timed_us(torch, lambda: wq.matmul(X, out=Y), 0.1)
+        tf = 2.0 * Mp * Kp * Np / us / 1e6
+        out["other_configs"].append({"workload": f"C4: {name} prefill, X[{Mp},{Kp}] bf16, W[{Kp},{Np}] 50% zeros",
+                                     "kernel": "tensor-core" if L.tllm_mma_launch_count() > m0 else "gather", "us_per_launch": us,
+                                     "dense_equivalent_TFLOPs": tf, "frac_of_bf16_peak": tf / peak_tc, "bf16_peak_TFLOPs": peak_tc,
+                                     "peak_source": kind, "check_rel_err": err})
+        wq.close()
     return out
 
 
 # ------------------------------------------------------------------------------------------------------
-# reference CPU arm
+# the tensor-parallel decoder
 # ------------------------------------------------------------------------------------------------------
-GEMV_CANDIDATES = [   # (group, kernel name, simd chunk of the format)
-    (64, "GEMV_CPU_FP32_rowMajor_TCSC_Merged_GroupMin_G64_AVX512_OpenMP", 0),
-    (128, "GEMV_CPU_FP32_rowMajor_TCSC_Merged_GroupMin_G128_CS16_AVX512_OpenMP", 16),
-    (32, "GEMV_CPU_FP32_rowMajor_TCSC_Merged_GroupMin_G32_AVX512_OpenMP", 0),
-    (64, "GEMV_CPU_FP32_rowMajor_TCSC_Merged_GroupMin_G64_AVX2_OpenMP", 0),
-]
+def decoder_bench(torch, dist, world, rank, device, steps, warmup, sparsities, batches, reduce, quick=False):
+    from ternaryllm_b200 import _lib
+    from ternaryllm_b200.tensor_parallel import PeerReduce, TernaryDecoderLayerTP, reference_decoder_layer
 
+    L = _lib.lib()
+    d = DEC
+    t_begin = time.time()
 
-def cpu_reference_run(weights, x_rows, steps, warmup, budget_s=25.0):
-    """Times the reference's CPU kernels (oracle/_ref: its GEMV family, GEMM_CPU_FP32.cpp:14879-16838) on the
-    given dense weights; falls back to the C restatement when the compiled reference cannot run here.
-    Returns (seconds per product, description dict)."""
-    import oracle
-
-    K, N = weights[0].shape
-    M = x_rows.shape[0]
-    r = oracle.ref()
-    cores = os.cpu_count() or 1
-    if r is None:
-        # C restatement, single thread: dense walk of the ternary matrix (oracle.c, orc_dense_f64)
-        w = weights[0]
-        t0 = time.perf_counter()
-        oracle.dense_f64(x_rows.astype(np.float64), w, 1.0)
-        dt = time.perf_counter() - t0
-        return dt, {"kind": "port", "cores": 1, "kernel": "orc_dense_f64", "sample": f"1 product of {M}x{K}x{N}, 1 thread"}
-    r.ref_set_threads(cores)
-    x32 = np.ascontiguousarray(x_rows.astype(np.float32))
-    best = None
-    t_begin = time.perf_counter()
-    for G, name, simd in GEMV_CANDIDATES:
-        if N % G or time.perf_counter() - t_begin > budget_s:
-            continue
-        fmts = []
-        for w in weights:
-            meta, ri = oracle.ref_merged_group(w, G, "min", False, simd)
-            fmts.append((meta, np.concatenate([ri.astype(np.int32), np.zeros(64, np.int32)])))
-        y = np.zeros(N, np.float32)
-
-        def one_pass():
-            for meta, ri32 in fmts:
-                for m in range(M):          # the reference's decode path is one GEMV per row
-                    oracle.ref_call("F4", name, x32[m], meta, ri32, y, N, K)
-
-        try:
-            for _ in range(max(1, warmup)):
-                one_pass()
-        except KeyError:
-            continue
-        n = 0
-        t0 = time.perf_counter()
-        while n < steps and time.perf_counter() - t0 < budget_s / len(GEMV_CANDIDATES):
-            one_pass()
-            n += 1
-        dt = (time.perf_counter() - t0) / (n * len(fmts))
-        if best is None or dt < best[0]:
-            best = (dt, name, n)
-    dt, name, n = best
-    return dt, {"kind": "reference", "cores": cores, "kernel": name,
-                "sample": f"{n} passes over {len(weights)} distinct weights of {K}x{N}, {M} row(s), best of {len(GEMV_CANDIDATES)} reference GEMV kernels"}
-
-
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5000)
-    ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--rows", type=int, default=1)
-    ap.add_argument("--sparsity", type=float, default=0.75)
-    ap.add_argument("--inners", type=int, default=K_IN, help="rows of W (K); the headline workload is 4096")
-    ap.add_argument("--columns", type=int, default=N_OUT, help="columns of W (N); the headline workload is 11008")
-    ap.add_argument("--copies", type=int, default=0, help="distinct packed weights per step (0 = enough to exceed 3x L2)")
-    ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-other-configs", action="store_true", help="skip the short measurements of the neighbouring configurations")
-    ap.add_argument("--prefill", action="store_true",
-                    help="time only the 13B-shape QKV prefill product on the tensor cores (X [2048,5120] bf16, W [5120,15360], 50 %% zeros)")
-    a = ap.parse_args()
-    a.warmup = max(a.warmup, 3)
-
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    M, K, N, S = a.rows, a.inners, a.columns, a.sparsity
-    shape_name = "Llama-7B up-projection shape" if (K, N) == (K_IN, N_OUT) else "custom shape"
-    workload = f"decode ternary SpMV, {shape_name}: x[{M},{K}] fp16 N(0,1), W[{K},{N}] ternary {S:.0%} zeros, fp16 scale U(0.01,0.05)"
-
-    if a.impl == "reference":
-        if rank != 0:
-            return 0
-        weights = [make_weight(1000 + i, K, N, S) for i in range(4)]
-        nnz = int(np.mean([(w != 0).sum() for w in weights]))
-        rng = np.random.default_rng(12345)
-        x = rng.standard_normal((M, K)).astype(np.float16)
-        dt, desc = cpu_reference_run(weights, x, a.steps, a.warmup, budget_s=120.0)
-        balg = algorithmic_bytes(nnz, K, N, M, 2)
-        gbps = balg / dt / 1e9
-        line = {"impl": "reference", "metric": METRIC, "value": gbps, "unit": "GB/s", "n_gpus": a.gpus, "steps": a.steps,
-                "warmup": a.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": "f32", "data": "synthetic",
-                "config": {"workload": workload, "step": "one product on the host cores", "algorithmic_bytes_per_product": balg},
-                "cpu_baseline": {"value": gbps, "unit": "GB/s", **desc},
-                "e2e": {"value": gbps, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
-        print(json.dumps(line))
-        return 0
-
-    import torch
-
-    from ternaryllm_b200 import PackedWeight, _lib
-
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (there is no CPU path in this library)")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=device)
-
-    if a.prefill:
-        Kp, Np, Mp = 5120, 15360, 2048
-        wq = PackedWeight.from_dense(make_weight(90, Kp, Np, 0.5), scale=0.02, device=device)
-        Xp = torch.randn((Mp, Kp), device=device).to(torch.bfloat16)
-        Yp = torch.empty((Mp, Np), dtype=torch.bfloat16, device=device)
-        for _ in range(a.warmup):
-            wq.matmul(Xp, out=Yp)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(a.steps):
-            wq.matmul(Xp, out=Yp)
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / a.steps
-        ref = (Xp[:64].double() @ torch.tensor(make_weight(90, Kp, Np, 0.5), device=device).double()) * 0.02
-        err = float((Yp[:64].double() - ref).abs().max() / ref.abs().max())
-        peak_tc, kind = measured_peak("bf16_tflops", 1590.0)
-        tf = 2.0 * Mp * Kp * Np / us / 1e6
-        print(json.dumps({"metric": "ternary_prefill_dense_equivalent_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": a.steps,
-                          "warmup": a.warmup, "ms_per_step": us / 1e3, "higher_is_better": True, "dtype": "bf16 x ternary, fp32 accumulate",
-                          "data": "synthetic", "config": {"workload": f"QKV prefill, X[{Mp},{Kp}] bf16, W[{Kp},{Np}] 50% zeros", "check_rel_err": err},
-                          "roofline": {"bound": "tensor", "achieved": tf, "peak": peak_tc, "unit": "TFLOP/s", "frac": tf / peak_tc, "peak_source": kind,
-                                       "traffic": None},
-                          "gpu_launches": a.steps}))
-        return 0
-
-    peak, peak_kind = measured_peak()
-    R = a.copies or max(4, -(-3 * L2_BYTES // (2 * int(K * N * (1 - S)))) + 1)
-    rng = np.random.default_rng(12345)
-    scales = [float(np.float16(v)) for v in rng.uniform(0.01, 0.05, R)]
-    packed, nnzs, w0 = [], [], None
-    for i in range(R):
-        w = make_weight(1000 + 100 * rank + i, K, N, S)
-        nnzs.append(int((w != 0).sum()))
-        packed.append(PackedWeight.from_dense(w, scale=scales[i], device=device))
-        if i == 0:
-            w0 = w
-    nnz = int(np.mean(nnzs))
-    info = packed[0].info
-    balg = algorithmic_bytes(nnz, K, N, M, 2)
-    bphys = info["stream_bytes"] + info["meta_bytes"] + 2 * M * (K + N)
-
-    x_host = torch.tensor(rng.standard_normal((M, K)), dtype=torch.float16).pin_memory()
-    X = x_host.to(device)
-    Y = [torch.empty((M, N), dtype=torch.float16, device=device) for _ in range(R)]
-
-    def step():
-        for i in range(R):
-            packed[i].matmul(X, out=Y[i])
-
-    # correctness guard inside the benchmark: compare one product with a dense fp64 product on the device
-    step()
-    torch.cuda.synchronize()
-    ref = (X.double() @ torch.tensor(w0, device=device).double()) * scales[0]
-    err = float((Y[0].double() - ref).abs().max() / ref.abs().max())
-    if not err <= 1e-3 + 2.0 ** -11:
-        raise SystemExit(f"benchmark output differs from the dense product (rel err {err})")
-
-    graph = None
-    if not a.no_graph:
-        try:
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                step()
-            torch.cuda.current_stream().wait_stream(side)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                step()
-        except Exception as e:      # keep measuring with plain launches
-            sys.stderr.write(f"[bench] CUDA graph capture failed ({e}); timing plain launches\n")
-            graph = None
-            torch.cuda.synchronize()
-    run = graph.replay if graph is not None else step
+    def note(msg):
+        sys.stderr.write(f"[bench rank {rank} +{time.time() - t_begin:6.1f}s] {msg}\n")
+        sys.stderr.flush()
 
     def barrier():
         torch.cuda.synchronize()
@@ -410,95 +308,310 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(a.warmup):
-        run()
-    barrier()
-    launches0 = _lib.lib().tllm_launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clk:
-        e0.record()
-        for _ in range(a.steps):
-            run()
-        e1.record()
+    peer = PeerReduce(max(batches), d["hidden"], device) if reduce == "peer" else None
+    records, clocks, headline = [], None, None
+    for S in sparsities:
+        # enough distinct layer weight sets per rank that a step streams every set from HBM (3x the L2 capacity)
+        layers = [TernaryDecoderLayerTP(d["hidden"], d["ffn"], d["heads"], d["kv_heads"], d["head_dim"], S, world, rank, device,
+                                        kv_len=d["kv_len"], max_batch=max(batches), seed=100, reduce=reduce, peer=peer)]
+        per_set = sum(i["stream_bytes"] + i["meta_bytes"] for i in (layers[0].qkv.info, layers[0].o.info, *layers[0].mlp.info))
+        nsets = 1 if quick else max(1, min(8, int(-(-3 * L2_BYTES // per_set))))
+        for i in range(1, nsets):
+            layers.append(TernaryDecoderLayerTP(d["hidden"], d["ffn"], d["heads"], d["kv_heads"], d["head_dim"], S, world, rank, device,
+                                                kv_len=d["kv_len"], max_batch=max(batches), seed=100 + 50 * i, reduce=reduce, peer=peer))
+        alg_local = float(np.mean([l.alg_bytes_local for l in layers])) * d["layers"]
+        note(f"{S:.0%} zeros: {nsets} layer weight set(s) packed ({per_set / 1e6:.0f} MB per set and rank)")
+
+        # ---- parity before timing: one layer on the N ranks against the dense fp32 layer on rank 0 ----
+        g = torch.Generator(device="cpu").manual_seed(7)
+        Mc = min(4, max(batches))
+        xc = torch.randn((Mc, d["hidden"]), generator=g).to(device, torch.bfloat16)
+        xs, pending = layers[0](xc.clone())
+        got = layers[0].finish(xs, pending).float()
+        torch.cuda.synchronize()
+        parity = None
+        if rank == 0:
+            want = reference_decoder_layer(layers[0].weights, xc.float(), d["kv_len"], max(batches), 100)
+            parity = float((got - want).abs().max() / want.abs().max())
+            del want
+            torch.cuda.empty_cache()
+            if not parity < 2e-2:
+                raise SystemExit(f"TP-{world} layer differs from the dense layer: rel err {parity}")
+            note(f"TP-{world} layer vs dense fp32 layer: rel err {parity:.2e}")
         barrier()
-    ms_total = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms_total], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / a.steps
-    us_launch = ms_step * 1e3 / R
-    gpu_launches = a.steps * R            # R kernel launches per step (replayed from a graph when one was captured)
-    value = world * R * balg / (ms_step * 1e-3) / 1e9
-    achieved = balg / (us_launch * 1e-6) / 1e9
-    for p in packed:
-        p.check()
 
-    # ---- end to end through the host-buffer entry point ----
-    y_host = [np.empty((M, N), np.float16) for _ in range(R)]
-    y_pin = [torch.from_numpy(y).pin_memory() for y in y_host]
-    e2e_steps = max(3, min(a.steps, 100))
+        for batch in batches:
+            g = torch.Generator(device="cpu").manual_seed(1)
+            x_host = torch.randn((batch, d["hidden"]), generator=g).to(torch.bfloat16).pin_memory()
+            x0 = x_host.to(device)
+            xw = torch.empty_like(x0)
+            y_host = torch.empty((batch, d["hidden"]), dtype=torch.bfloat16).pin_memory()
 
-    def e2e_step():
-        for i in range(R):
-            _lib.check(_lib.lib().tllm_spmm_host(packed[i]._h, x_host.data_ptr(), _lib.F16, _lib.ROW_MAJOR, M, y_pin[i].data_ptr(),
-                                                 _lib.F16, _lib.ROW_MAJOR))
+            result = {}
 
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
+            def step():
+                xw.copy_(x0)                          # the layers update the residual stream in place
+                x, pending = xw, None
+                for i in range(d["layers"]):
+                    x, pending = layers[i % nsets](x, pending)
+                result["y"] = layers[0].finish(x, pending)
+
+            n0, m0 = L.tllm_launch_count(), L.tllm_mma_launch_count()
+            step()
+            torch.cuda.synchronize()
+            launches, tensor_launches = L.tllm_launch_count() - n0, L.tllm_mma_launch_count() - m0
+            assert torch.isfinite(result["y"].float()).all()
+            graph = capture(torch, step)
+            y = result["y"]                           # the tensor the captured step writes
+            for _ in range(max(3, warmup)):
+                graph.replay()
+            barrier()
+            nsteps = steps if steps > 0 else (10 if quick else 20)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with ClockSampler(device.index) as clk:
+                e0.record()
+                for _ in range(nsteps):
+                    graph.replay()
+                e1.record()
+                barrier()
+            ms = e0.elapsed_time(e1) / nsteps
+            # end to end: the token's activations come from pinned host memory and the result goes back, every step
+            def e2e_step():
+                x0.copy_(x_host, non_blocking=True)
+                graph.replay()
+                y_host.copy_(y, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+
+            for _ in range(2):
+                e2e_step()
+            barrier()
+            t0 = time.perf_counter()
+            n_e2e = max(3, nsteps // 2)
+            for _ in range(n_e2e):
+                e2e_step()
+            dt_e2e = (time.perf_counter() - t0) / n_e2e
+            if world > 1:
+                t = torch.tensor([ms, dt_e2e], device=device, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms, dt_e2e = float(t[0]), float(t[1])
+            rec = {"zeros": S, "batch": batch, "tokens_per_s": batch / (ms * 1e-3), "ms_per_step": ms, "steps": nsteps,
+                   "e2e_tokens_per_s": batch / dt_e2e, "launches_per_step": int(launches), "tensor_core_launches_per_step": int(tensor_launches),
+                   "weight_sets": nsets, "algorithmic_weight_GBps_per_rank": alg_local / (ms * 1e-3) / 1e9, "parity_rel_err": parity,
+                   "h2d_bytes_per_step": batch * d["hidden"] * 2, "d2h_bytes_per_step": batch * d["hidden"] * 2}
+            if headline is None:
+                headline, clocks = rec, clk.summary()
+                rec["breakdown_us_per_layer"] = layer_breakdown(torch, layers[0], x0, reduce)
+            records.append(rec)
+            note(f"{S:.0%} zeros, batch {batch}: {rec['tokens_per_s']:.1f} tokens/s ({ms:.2f} ms/step)")
+            del graph
+            torch.cuda.synchronize()
+        for l in layers:
+            l.qkv.close(), l.o.close(), l.mlp.close()
+        del layers
+        torch.cuda.empty_cache()
+    if peer is not None:
+        peer.check()
+    return headline, records, clocks
+
+
+def layer_breakdown(torch, layer, x0, reduce, reps=20):
+    """CUDA-event times of the phases of one layer (eager launches, averaged): where a step's time goes."""
+    M = x0.shape[0]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(7)] for _ in range(reps)]
+    x = x0.clone()
+    pending = layer._part2[:M].zero_() if reduce == "peer" else torch.zeros_like(x)
+    from ternaryllm_b200.tensor_parallel import add_rms_norm, all_reduce_sum
+
+    for r in range(reps):
+        e = ev[r]
+        e[0].record()
+        h = layer.peer.reduce(pending, x) if reduce == "peer" else add_rms_norm(x, all_reduce_sum(pending))
+        e[1].record()
+        qkv = layer.qkv.matmul(h)
+        e[2].record()
+        a = layer.attention(qkv, M)
+        e[3].record()
+        o = layer.o.matmul(a, out=layer._part[:M]) if reduce == "peer" else layer.o.matmul(a)
+        e[4].record()
+        h2 = layer.peer.reduce(o, x) if reduce == "peer" else add_rms_norm(x, all_reduce_sum(o))
+        e[5].record()
+        pending = layer.mlp.forward(h2, out=layer._part2[:M]) if reduce == "peer" else layer.mlp.forward(h2)
+        e[6].record()
     torch.cuda.synchronize()
-    dt_e2e = (time.perf_counter() - t0) / e2e_steps
-    if world > 1:
-        t = torch.tensor([dt_e2e], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt_e2e = float(t.item())
-    e2e_val = world * R * balg / dt_e2e / 1e9
-    err2 = float((y_pin[0].to(device).double() - ref).abs().max() / ref.abs().max())
-    if not err2 <= 1e-3 + 2.0 ** -11:
-        raise SystemExit(f"host-buffer path differs from the dense product (rel err {err2})")
+    names = ["reduce+add+norm (MLP)", "QKV product", "attention core and cache write (stock)", "O product", "reduce+add+norm (attention)", "MLP products"]
+    return {n: float(np.median([ev[r][i].elapsed_time(ev[r][i + 1]) for r in range(3, reps)])) * 1e3 for i, n in enumerate(names)}
 
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+
+# ------------------------------------------------------------------------------------------------------
+# reference CPU arm: the reference's own kernels on the host cores, bounded sample
+# ------------------------------------------------------------------------------------------------------
+GEMV_CANDIDATES = [   # (group, kernel name, simd chunk of the format)
+    (64, "GEMV_CPU_FP32_rowMajor_TCSC_Merged_GroupMin_G64_AVX512_OpenMP", 0),
+    (128, "GEMV_CPU_FP32_rowMajor_TCSC_Merged_GroupMin_G128_CS16_AVX512_OpenMP", 16),
+    (64, "GEMV_CPU_FP32_rowMajor_TCSC_Merged_GroupMin_G64_AVX2_OpenMP", 0),
+]
+
+
+def cpu_decoder_sample(budget_s=25.0, sparsity=0.5, slice_div=8):
+    """Tokens/s of the decoder step at batch 1 on the host cores with the reference's GEMV kernels (oracle/_ref:
+    GEMM_CPU_FP32.cpp:14879-16838), from a bounded sample: a 1/slice_div column slice of each of one layer's five
+    linears (same rows, same sparsity), timed and scaled to the full width and to the layer count.  The attention core
+    and the norms are left out (they are not the reference's ternary path).  Falls back to the C restatement's dense
+    walk when the compiled reference cannot run on this host."""
+    import oracle
+
+    d = DEC
+    cores = os.cpu_count() or 1
+    shapes = [(d["hidden"], (d["heads"] + 2 * d["kv_heads"]) * d["head_dim"]), (d["heads"] * d["head_dim"], d["hidden"]),
+              (d["hidden"], d["ffn"]), (d["hidden"], d["ffn"]), (d["ffn"], d["hidden"])]
+    r = oracle.ref()
+    rng = np.random.default_rng(3)
+    if r is None:
+        K, N = shapes[0][0], shapes[0][1] // slice_div
+        w = make_weight(1, K, N, sparsity)
+        x = rng.standard_normal((1, K))
+        t0 = time.perf_counter()
+        oracle.dense_f64(x, w, 1.0)
+        dt = (time.perf_counter() - t0) * slice_div
+        total = dt * sum(k * n for k, n in shapes) / (shapes[0][0] * shapes[0][1]) * d["layers"]
+        return 1.0 / total, {"kind": "port", "cores": 1, "kernel": "orc_dense_f64",
+                             "sample": f"one {K}x{N} slice, 1 thread, scaled to the five linears of {d['layers']} layers"}
+    r.ref_set_threads(cores)
+    best = None
+    t_begin = time.perf_counter()
+    for G, name, simd in GEMV_CANDIDATES:
+        if time.perf_counter() - t_begin > budget_s:
+            break
+        per_layer, ok = 0.0, True
+        for (K, N) in shapes:
+            Ns = max(G, N // slice_div // G * G)
+            w = make_weight(K + N, K, Ns, sparsity)
+            meta, ri = oracle.ref_merged_group(w, G, "min", False, simd)
+            ri32 = np.concatenate([ri.astype(np.int32), np.zeros(64, np.int32)])
+            x = np.ascontiguousarray(rng.standard_normal(K).astype(np.float32))
+            y = np.zeros(Ns, np.float32)
+            try:
+                oracle.ref_call("F4", name, x, meta, ri32, y, Ns, K)
+            except KeyError:
+                ok = False
+                break
+            n, t0 = 0, time.perf_counter()
+            while n < 3 or (time.perf_counter() - t0 < 0.5 and n < 50):
+                oracle.ref_call("F4", name, x, meta, ri32, y, Ns, K)
+                n += 1
+            per_layer += (time.perf_counter() - t0) / n * (N / Ns)
+        if ok and (best is None or per_layer < best[0]):
+            best = (per_layer, name)
+    per_layer, name = best
+    return 1.0 / (per_layer * d["layers"]), {
+        "kind": "reference", "cores": cores, "kernel": name,
+        "sample": f"1/{slice_div} column slice of each of one layer's five linears ({sparsity:.0%} zeros), best of the reference GEMV kernels, "
+                  f"scaled to full width and {d['layers']} layers; attention core and norms not included"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=0, help="timed decoder steps per configuration (0 = 20)")
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--reduce", default="peer", choices=["peer", "nccl"], help="how the row-sharded products are summed over the ranks")
+    ap.add_argument("--quick", action="store_true", help="one weight set, 50 %% zeros only, short product sweep (for smoke runs)")
+    ap.add_argument("--no-spmv", action="store_true", help="skip the stand-alone product measurements")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--spmv-only", action="store_true", help="only the stand-alone headline product (for profiler captures)")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    d = DEC
+    workload = (f"tensor-parallel ternary Llama-70B-shaped decoder: hidden {d['hidden']}, FFN {d['ffn']}, {d['heads']}q/{d['kv_heads']}kv x {d['head_dim']}, "
+                f"{d['layers']} layers, 50% zeros, bf16 activations, KV length {d['kv_len']}, decode batch 1")
+
+    if a.impl == "reference":
+        if rank != 0:
+            return 0
+        tps, desc = cpu_decoder_sample(budget_s=120.0)
+        line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+                "ms_per_step": 1e3 / tps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": workload, "step": "one token through the linears of all layers on the host cores (sampled)"},
+                "cpu_baseline": {"value": tps, "unit": "tokens/s", **desc},
+                "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+        print(json.dumps(line))
         return 0
 
-    line = {
-        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
-        "config": {"workload": workload, "step": f"one decode token through {R} distinct packed weights ({R} launches)",
-                   "l2": f"inputs larger than L2: {R} weights x {bphys / 1e6:.1f} MB rotate through a {L2_BYTES >> 20} MiB L2",
-                   "algorithmic_bytes_per_launch": balg, "physical_bytes_per_launch": bphys, "nnz": nnz,
-                   "us_per_launch": us_launch, "cuda_graph": graph is not None, "pdl": os.environ.get("TLLM_PDL", "1") != "0",
-                   "accumulate": "fp32", "check_rel_err": err,
-                   "pack": {k: info[k] for k in ("tile_rows", "tiles", "col_blocks", "k_splits", "num_ctas", "units")}},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "frac_physical": (bphys / (us_launch * 1e-6) / 1e9) / peak, "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
-                     "traffic": NCU_TRAFFIC_BYTES if (M == 1 and S == 0.75 and (K, N) == (K_IN, N_OUT)) else None},
-        "clocks": clk.summary(),
-        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": R * 2 * M * K, "d2h_bytes_per_step": R * 2 * M * N,
-                "us_per_call": dt_e2e * 1e6 / R, "steps": e2e_steps},
-        "gpu_launches": gpu_launches,
-    }
-    if world == 1 and not a.no_cpu_baseline:
-        try:
-            cw = [w0] + [make_weight(1000 + i, K, N, S) for i in range(1, 4)]
-            dt, desc = cpu_reference_run(cw, x_host.numpy(), 10, 3, budget_s=20.0)
-            line["cpu_baseline"] = {"value": balg / dt / 1e9, "unit": "GB/s", "us_per_product": dt * 1e6, **desc}
-        except Exception as e:
-            line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
-    if world == 1 and not a.no_other_configs:
-        try:
-            line["other_configs"] = other_configs(torch, device, packed, nnz, K, N, peak)
-        except Exception as e:
-            line["other_configs"] = [{"failed": str(e)}]
-    print(json.dumps(line))
+    import torch
+
+    from ternaryllm_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path in this library)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
     if world > 1:
-        dist.destroy_process_group()
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    peak, peak_kind = measured_peak()
+
+    if a.spmv_only:
+        rec = spmv_records(torch, device, peak, quick=True)["headline"]
+        print(json.dumps(rec))
+        return 0
+
+    sparsities = (0.5,) if (a.quick or world > 1) else (0.5, 0.7, 0.9)
+    batches = (1, 16, 64)
+    headline, records, clocks = decoder_bench(torch, dist, world, rank, device, a.steps, a.warmup, sparsities, batches, a.reduce, quick=a.quick)
+
+    spmv = None
+    if rank == 0 and not a.no_spmv:
+        spmv = spmv_records(torch, device, peak, quick=a.quick or world > 1)
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": headline["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": headline["steps"], "warmup": a.warmup,
+            "ms_per_step": headline["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 activations, ternary weights, fp32 sums", "data": "synthetic",
+            "config": {"workload": workload, "parallelism": f"tp{world}", "reduce": a.reduce,
+                       "step": f"one token through {d['layers']} layers ({headline['launches_per_step']} kernel launches of this library, one CUDA graph)",
+                       "l2": f"inputs larger than L2: {headline['weight_sets']} distinct layer weight set(s) per rank, cycled through the layers",
+                       "parity_rel_err_vs_dense_layer": headline["parity_rel_err"]},
+            "clocks": clocks,
+            "e2e": {"value": headline["e2e_tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": headline["h2d_bytes_per_step"],
+                    "d2h_bytes_per_step": headline["d2h_bytes_per_step"]},
+            "gpu_launches": int(headline["launches_per_step"]) * int(headline["steps"]),
+            "decoder": records,
+        }
+        if spmv is not None:
+            h = spmv["headline"]
+            line["roofline"] = {"bound": "hbm", "achieved": h["algorithmic_GBps"], "peak": peak, "unit": "GB/s", "frac": h["frac"],
+                                "frac_physical": h["frac_physical"], "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
+                                "kernel": "bstream_spmm_kernel<float,1>", "us_per_launch": h["us_per_launch"],
+                                "workload": f"decode product x[1,{K_IN}] fp16, W[{K_IN},{N_OUT}] 75% zeros, {h['weights_in_rotation']} weights in rotation (larger than L2)",
+                                "algorithmic_bytes_per_launch": h["algorithmic_bytes"], "physical_bytes_per_launch": h["physical_bytes"],
+                                "traffic": NCU_TRAFFIC["bytes"], "traffic_source": NCU_TRAFFIC["source"]}
+            line["spmv"] = spmv
+        if world == 1 and not a.no_cpu_baseline:
+            try:
+                tps, desc = cpu_decoder_sample(budget_s=25.0)
+                line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", **desc}
+            except Exception as e:
+                line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        # Leave without tearing the communicator down: destroying a process group right after graph replays that
+        # used peer-mapped memory is not needed, and the processes end here anyway.
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 

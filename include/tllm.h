@@ -243,6 +243,9 @@ int tllm_mlp_destroy(tllm_mlp* m);
 /* X [rows][hidden] -> Y [rows][hidden]; H (device, rows*intermediate elements of x_dtype) receives the
  * intermediate activations and may be NULL to use the handle's own buffer. */
 int tllm_mlp_forward(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y, void* H, void* stream);
+/* Same with the result type chosen by the caller (TLLM_F32 keeps the down projection's sums unrounded: what a
+ * tensor-parallel layer hands to the all-reduce). */
+int tllm_mlp_forward_ex(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y, int y_dtype, void* H, void* stream);
 /* Same with HOST buffers and the reference's in-place convention (TernaryMLP<T>::forward overwrites its input with the
  * block's output, LlamaModel.hpp:343-452): X [rows][hidden] row-major is copied to the device, the block runs, the
  * result is copied back over X; H (host, rows*intermediate values, may be NULL) receives silu(gate)*up. Synchronises. */

@@ -65,6 +65,7 @@ SIGNATURES = {
     "tllm_mlp_create": (_I, [_P, _P, _P, _I, _I, _F, _F, _F, _P, _P]),
     "tllm_mlp_destroy": (_I, [_P]),
     "tllm_mlp_forward": (_I, [_P, _P, _I, _I, _P, _P, _P]),
+    "tllm_mlp_forward_ex": (_I, [_P, _P, _I, _I, _P, _I, _P, _P]),
     "tllm_mlp_forward_host": (_I, [_P, _P, _I, _I, _P]),
     "tllm_mlp_get_info": (_I, [_P, _P, _P]),
     "tllm_silu_mul": (_I, [_P, _P, _I, _L, _P]),

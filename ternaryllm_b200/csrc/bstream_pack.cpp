@@ -6,8 +6,10 @@
 // balanced by non-zero count (the reference's tile reordering by list length is computed and never used by its
 // kernels, ter_spmm_kernel.cuh:159-160).
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../../include/tllm.h"
@@ -73,9 +75,8 @@ bool simulate_unit(const LaneStream (&ls)[32], uint32_t lists, std::vector<uint1
 
 struct Builder {
     const ColumnLists<int8_t>& cl;
-    BsHostImage* out;
-    int T;                     // rows of a K-tile
-    size_t block_base = 0;     // first byte of the current block's stream
+    std::vector<uint8_t>* stream;   // the current block's stream (starts at byte 0)
+    int T;                          // rows of a K-tile
     LaneStream ls[32];
     std::vector<uint16_t> rp;
     std::vector<uint8_t> bucket[32];
@@ -114,13 +115,13 @@ struct Builder {
             min_nv = std::min(min_nv, ls[l].nvec());
             max_nv = std::max(max_nv, ls[l].nvec());
         }
-        std::vector<uint8_t>& s = out->stream;
-        while ((s.size() - block_base) % 128) s.push_back(0);
+        std::vector<uint8_t>& s = *stream;
+        while (s.size() % 128) s.push_back(0);
         const size_t unit_base = s.size();
         for (uint32_t i = 0; i < min_nv; ++i)
             for (int l = 0; l < 32; ++l) s.insert(s.end(), ls[l].bytes.begin() + (size_t)i * 16, ls[l].bytes.begin() + (size_t)(i + 1) * 16);
         for (int l = 0; l < 32; ++l) s.insert(s.end(), ls[l].bytes.begin() + (size_t)min_nv * 16, ls[l].bytes.end());
-        meta->push_back((uint32_t)((unit_base - block_base) / 16));
+        meta->push_back((uint32_t)(unit_base / 16));
         meta->push_back((uint32_t)(a - c_block0) | ((uint32_t)(b - a) << 16));
         meta->push_back((uint32_t)(t - t_block0) | ((uint32_t)rp.size() << 8));
         meta->push_back(min_nv | (max_nv << 16));
@@ -208,24 +209,27 @@ const char* bs_pack_dense(const int8_t* w, int inners, int columns, const tllm_p
         L.num_ctas = col_blocks * ks;
         L.max_cols_per_block = widest;
         L.cta.assign((size_t)L.num_ctas, TsCtaDesc{});
-        out->stream.clear();
-        out->meta.clear();
-        L.units = 0;
-        Builder bld{cl, out, T};
-        bool too_big = false;
-        std::vector<uint32_t> meta;
-        std::vector<int64_t> wprefix;
-        std::vector<int32_t> wstart;
-        for (int j = 0; j < ks && !too_big; ++j)
-            for (int b = 0; b < col_blocks && !too_big; ++b) {
+        struct BlockImage {
+            std::vector<uint8_t> stream;
+            std::vector<uint32_t> meta;
+            int units = 0;
+        };
+        std::vector<BlockImage> blocks((size_t)L.num_ctas);
+        std::atomic<int> next{0};
+        std::atomic<bool> too_big{false};
+        // blocks are independent: they are packed by as many threads as the host offers, then laid end to end
+        auto work = [&]() {
+            Builder bld{cl, nullptr, T};
+            std::vector<int64_t> wprefix;
+            std::vector<int32_t> wstart;
+            for (;;) {
+                const int id = next.fetch_add(1);
+                if (id >= L.num_ctas || too_big.load()) return;
+                const int j = id / col_blocks, b = id % col_blocks;
+                BlockImage& B = blocks[(size_t)id];
+                bld.stream = &B.stream;
                 const int c0 = L.col_start[b], c1 = L.col_start[b + 1];
                 const int t0 = j * tpc, t1 = std::min(tiles, t0 + tpc);
-                while (out->stream.size() % 512) out->stream.push_back(0);
-                while (out->meta.size() % 4) out->meta.push_back(0);
-                bld.block_base = out->stream.size();
-                TsCtaDesc& d = L.cta[(size_t)j * col_blocks + b];
-                d.stream_off = (uint32_t)(bld.block_base / 16);
-                d.meta_off = (uint32_t)out->meta.size();
                 // warp ranges by the non-zeros inside this block's tiles
                 wprefix.assign((size_t)(c1 - c0) + 1, 0);
                 for (int c = c0; c < c1; ++c) {
@@ -240,30 +244,49 @@ const char* bs_pack_dense(const int8_t* w, int inners, int columns, const tllm_p
                     wprefix[(size_t)(c - c0) + 1] = wprefix[(size_t)(c - c0)] + n;
                 }
                 balanced_even_cuts(wprefix, c1 - c0, BS_WARPS, &wstart);
+                std::vector<uint32_t>& meta = B.meta;
                 meta.assign(BS_BLOCK_HEADER + BS_WARPS + 1, 0u);
                 meta[0] = (uint32_t)c0, meta[1] = (uint32_t)(c1 - c0), meta[2] = (uint32_t)t0, meta[3] = (uint32_t)(t1 - t0);
                 meta[4] = (uint32_t)j, meta[5] = (uint32_t)b;
-                int units = 0;
                 for (int wi = 0; wi < BS_WARPS; ++wi) {
                     meta[BS_BLOCK_HEADER + wi] = (uint32_t)meta.size();
-                    for (int t = t0; t < t1; ++t) bld.emit_units(t, c0 + wstart[wi], c0 + wstart[wi + 1], c0, t0, &meta, &units);
+                    for (int t = t0; t < t1; ++t) bld.emit_units(t, c0 + wstart[wi], c0 + wstart[wi + 1], c0, t0, &meta, &B.units);
                 }
                 meta[BS_BLOCK_HEADER + BS_WARPS] = (uint32_t)meta.size();
-                meta[6] = (uint32_t)units;
+                meta[6] = (uint32_t)B.units;
                 while (meta.size() % 4) meta.push_back(0);
-                if (meta.size() * 4 > BS_MAX_META_BYTES) {
-                    too_big = true;
-                    break;
-                }
-                out->meta.insert(out->meta.end(), meta.begin(), meta.end());
-                d.meta_words = (uint32_t)meta.size();
-                while ((out->stream.size() - bld.block_base) % 512) out->stream.push_back(0);
-                d.nvec = (uint32_t)((out->stream.size() - bld.block_base) / 16);
-                L.units += units;
+                if (meta.size() * 4 > BS_MAX_META_BYTES) too_big.store(true);
+                while (B.stream.size() % 512) B.stream.push_back(0);
             }
-        if (too_big) {
+        };
+        unsigned nthreads = std::thread::hardware_concurrency();
+        nthreads = std::max(1u, std::min(nthreads, 32u));
+        nthreads = std::min<unsigned>(nthreads, (unsigned)L.num_ctas);
+        std::vector<std::thread> pool;
+        for (unsigned i = 1; i < nthreads; ++i) pool.emplace_back(work);
+        work();
+        for (std::thread& th : pool) th.join();
+        if (too_big.load()) {
             col_blocks = std::min((columns + 1) / 2, std::max(col_blocks + 1, (int)((int64_t)col_blocks * 3 / 2)));
             continue;
+        }
+        out->stream.clear();
+        out->meta.clear();
+        L.units = 0;
+        size_t total_stream = 0, total_meta = 0;
+        for (const BlockImage& B : blocks) total_stream += B.stream.size(), total_meta += B.meta.size();
+        out->stream.reserve(total_stream);
+        out->meta.reserve(total_meta);
+        for (int id = 0; id < L.num_ctas; ++id) {
+            const BlockImage& B = blocks[(size_t)id];
+            TsCtaDesc& d = L.cta[(size_t)id];
+            d.stream_off = (uint32_t)(out->stream.size() / 16);
+            d.nvec = (uint32_t)(B.stream.size() / 16);
+            d.meta_off = (uint32_t)out->meta.size();
+            d.meta_words = (uint32_t)B.meta.size();
+            out->stream.insert(out->stream.end(), B.stream.begin(), B.stream.end());
+            out->meta.insert(out->meta.end(), B.meta.begin(), B.meta.end());
+            L.units += B.units;
         }
         break;
     }

@@ -907,7 +907,12 @@ int tllm_mlp_destroy(tllm_mlp* m) {
 }
 
 int tllm_mlp_forward(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y, void* H, void* stream) {
+    return tllm_mlp_forward_ex(m, X, x_dtype, rows, Y, x_dtype, H, stream);
+}
+
+int tllm_mlp_forward_ex(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y, int y_dtype, void* H, void* stream) {
     if (!m || !X || !Y) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: NULL pointer");
+    if (y_dtype != TLLM_F32 && y_dtype != TLLM_F16 && y_dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: unsupported y_dtype");
     if (rows <= 0) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: rows must be positive");
     if (x_dtype != TLLM_F32 && x_dtype != TLLM_F16 && x_dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: unsupported dtype");
     if (!H && (size_t)rows * m->inter * dtype_size(x_dtype) > m->h_cap) return fail(TLLM_ERR_ARG, "tllm_mlp_forward: pass H for more than 16 rows");
@@ -918,12 +923,12 @@ int tllm_mlp_forward(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y,
     if (mm_usable(m->gate_up, X, x_dtype, TLLM_ROW_MAJOR, m->hidden, rows) && mm_usable(m->down, h, x_dtype, TLLM_ROW_MAJOR, m->inter, rows)) {
         rc = run_mm(m->gate_up, X, x_dtype, m->hidden, rows, h, x_dtype, m->inter, 1, m->s_gate, m->s_up, st);
         if (rc) return rc;
-        return run_mm(m->down, h, x_dtype, m->inter, rows, Y, x_dtype, m->hidden, 0, m->down->scale, 0.f, st);
+        return run_mm(m->down, h, x_dtype, m->inter, rows, Y, y_dtype, m->hidden, 0, m->down->scale, 0.f, st);
     }
     rc = run_gather(m->gate_up, X, x_dtype, TLLM_ROW_MAJOR, m->hidden, rows, h, x_dtype, m->inter, 1, m->s_gate, m->s_up,
                     Scratch{m->gate_up->d_partial, m->gate_up->d_counters}, st);
     if (rc) return rc;
-    return run_gather(m->down, h, x_dtype, TLLM_ROW_MAJOR, m->inter, rows, Y, x_dtype, m->hidden, 0, m->down->scale, 0.f,
+    return run_gather(m->down, h, x_dtype, TLLM_ROW_MAJOR, m->inter, rows, Y, y_dtype, m->hidden, 0, m->down->scale, 0.f,
                       Scratch{m->down->d_partial, m->down->d_counters}, st);
 }
 

@@ -16,3 +16,16 @@ def make_weight(seed: int, K: int, N: int, sparsity: float) -> np.ndarray:
     w[(r >= z) & (r < z + half)] = -1
     w[r >= z + half] = 1
     return w
+
+
+def block_weight(seed: int, K: int, N: int, sparsity: float, axis: int, nblocks: int, first: int = 0, count: int | None = None) -> np.ndarray:
+    """Blocks [first, first + count) of a seeded ternary matrix [K, N] that is defined as the concatenation of `nblocks`
+    independently seeded blocks along `axis` (0: row blocks, 1: column blocks).  A tensor-parallel rank generates
+    only the blocks it holds, and every partitioning of the blocks sees the same matrix."""
+    if count is None:
+        count = nblocks - first
+    if (N if axis else K) % nblocks:
+        raise ValueError("the blocked axis does not divide into the blocks")
+    shape = (K, N // nblocks) if axis else (K // nblocks, N)
+    parts = [make_weight(seed * 1009 + b, shape[0], shape[1], sparsity) for b in range(first, first + count)]
+    return np.ascontiguousarray(np.concatenate(parts, axis=axis))

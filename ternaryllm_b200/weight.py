@@ -199,12 +199,14 @@ class PackedMLP:
         rows = x.shape[0]
         if out is None:
             out = torch.empty((rows, self.hidden), device=x.device, dtype=x.dtype)
+        elif out.dtype not in (x.dtype, torch.float32) or tuple(out.shape) != (rows, self.hidden) or not out.is_contiguous():
+            raise RuntimeError("out has the wrong dtype, shape or strides")
         if h is None and rows > 16:
             h = torch.empty((rows, self.inter), device=x.device, dtype=x.dtype)
         with torch.cuda.device(x.device):
-            check(lib().tllm_mlp_forward(self._h, x.data_ptr(), _lib.torch_dtype_code(x.dtype), rows, out.data_ptr(),
-                                         h.data_ptr() if h is not None else None, torch.cuda.current_stream().cuda_stream),
-                  "tllm_mlp_forward")
+            check(lib().tllm_mlp_forward_ex(self._h, x.data_ptr(), _lib.torch_dtype_code(x.dtype), rows, out.data_ptr(),
+                                            _lib.torch_dtype_code(out.dtype), h.data_ptr() if h is not None else None,
+                                            torch.cuda.current_stream().cuda_stream), "tllm_mlp_forward")
         return out
 
     def close(self):

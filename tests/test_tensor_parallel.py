@@ -1,6 +1,13 @@
-"""Tensor-parallel sharding logic on two CPU ranks (gloo): column shards concatenate to the full product, row
-shards all-reduce to it.  The packed GPU product is replaced by the oracle's dense product here (tests only);
-the GPU path of the same classes is covered by the decoder benchmark on real devices."""
+"""Tensor-parallel partitioning.
+
+CPU (gloo, two ranks): column shards concatenate to the full product, row shards all-reduce to it -- the packed GPU
+product is replaced by the oracle's dense product there -- and the blocked weight generator gives every
+tensor-parallel degree the same model.
+GPU (one device): the decoder layer against the same layer in dense fp32 PyTorch, with both reduction paths; the
+peer all-reduce kernel against a stand-in peer whose slot and flag the host fills, and its bounded wait when the
+flag is withheld (the kernel gives up after the limit, reports through the status word, and the context stays
+usable).  The multi-GPU run of the same code is bench.py under torch.distributed.run, which asserts TP-N against the
+dense layer before it times anything."""
 import os
 import socket
 
@@ -86,106 +93,148 @@ def test_shard_errors():
         shard_rows(w, 3, 0)
 
 
-@pytest.mark.gpu
-def test_decoder_layer_single_rank_matches_fp32_reference():
-    """One decode step of the Llama-shaped layer (fused QKV, grouped-query attention over a synthetic cache, O,
-    fused MLP) against the same arithmetic in plain fp32 PyTorch on dense weights.  Tolerance 2e-2 relative to the
-    largest output: the layer rounds to bf16 between its stages, the reference does not."""
-    import torch.nn.functional as F
+def test_blocked_weights_are_the_same_model_at_every_degree():
+    from ternaryllm_b200.tensor_parallel import DecoderWeights
 
-    from ternaryllm_b200.synthetic import make_weight
-    from ternaryllm_b200.tensor_parallel import TernaryDecoderLayerTP, rms_norm
+    W = DecoderWeights(256, 512, 8, 2, 16, 0.5, seed=3)
+    for name, axis in (("q", 1), ("o", 0), ("gate", 1), ("up", 1), ("down", 0)):
+        full = getattr(W, name)()
+        for world in (2, 4, 8):
+            parts = [getattr(W, name)(world, r) for r in range(world)]
+            assert np.array_equal(np.concatenate(parts, axis=axis), full), (name, world)
+    for which in (0, 1):
+        full = W.kv(which)
+        assert full.shape == (256, 32)
+        assert np.array_equal(np.concatenate([W.kv(which, 2, r) for r in range(2)], axis=1), full)
+        # more ranks than KV heads: neighbouring ranks hold the same head
+        for r in range(8):
+            assert np.array_equal(W.kv(which, 8, r), full[:, (r // 4) * 16:(r // 4 + 1) * 16])
+    assert abs((W.gate() == 0).mean() - 0.5) < 0.02
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("reduce", ["peer", "nccl"])
+def test_decoder_layer_single_rank_matches_dense_reference(reduce):
+    """One decode step of the Llama-shaped layer (fused QKV, grouped-query attention over a synthetic cache, O, fused
+    MLP, the reduction glue with world = 1) against the same layer with dense fp32 matrices.  Tolerance 2e-2 relative
+    to the largest output: both round to bf16 between their stages, at slightly different places."""
+    from ternaryllm_b200.tensor_parallel import TernaryDecoderLayerTP, reference_decoder_layer
 
     dev = torch.device("cuda", 0)
     hidden, ffn, hq, hkv, hd, S, M, L = 1024, 2816, 8, 2, 128, 0.5, 3, 64
-    layer = TernaryDecoderLayerTP(hidden, ffn, hq, hkv, hd, S, 1, 0, dev, kv_len=L, max_batch=4, seed=40, make_weight=make_weight)
+    layer = TernaryDecoderLayerTP(hidden, ffn, hq, hkv, hd, S, 1, 0, dev, kv_len=L, max_batch=4, seed=40, reduce=reduce)
     g = torch.Generator(device="cpu").manual_seed(5)
     x = torch.randn((M, hidden), generator=g).to(dev, torch.bfloat16)
-    xs, delta = layer(x.clone())
-    got = (xs + delta).float()
+    want = reference_decoder_layer(layer.weights, x.float(), L, 4, 40)
+    xs, pending = layer(x.clone())
+    got = layer.finish(xs, pending).float()
     torch.cuda.synchronize()
-
-    def W(i, k, n):
-        return torch.tensor(make_weight(40 + i, k, n, S), dtype=torch.float32, device=dev) * 0.02
-
-    xf = x.float()
-    h = rms_norm(xf)
-    q, k, v = h @ W(1, hidden, hq * hd), h @ W(2, hidden, hkv * hd), h @ W(3, hidden, hkv * hd)
-    kc, vc = layer.k_cache[:M].float().clone(), layer.v_cache[:M].float().clone()
-    kc[:, :, L], vc[:, :, L] = k.view(M, hkv, hd), v.view(M, hkv, hd)
-    a = F.scaled_dot_product_attention(q.view(M, hq, 1, hd), kc.repeat_interleave(hq // hkv, 1), vc.repeat_interleave(hq // hkv, 1))
-    x1 = (xf + a.reshape(M, hq * hd) @ W(4, hq * hd, hidden)).bfloat16().float()    # the stream is stored in bf16
-    h2 = rms_norm(x1)
-    want = x1 + (F.silu(h2 @ W(5, hidden, ffn)) * (h2 @ W(6, hidden, ffn))) @ W(7, ffn, hidden)
     err = (got - want).abs().max().item() / want.abs().max().item()
     assert err < 2e-2, err
+    # two layers in a row: the pending MLP output travels into the next layer's fused add + norm
+    xs, pending = layer(x.clone())
+    xs, pending = layer(xs, pending)
+    assert torch.isfinite(layer.finish(xs, pending).float()).all()
+    if layer.peer is not None:
+        layer.peer.check()
+
+
+def _comm(world, rank, rows, hidden):
+    import ctypes as C
+
+    from ternaryllm_b200 import _lib
+
+    h = C.c_void_p()
+    _lib.check(_lib.lib().tllm_comm_create(world, rank, rows, hidden, C.byref(h)))
+    return h
 
 
 @pytest.mark.gpu
-def test_attention_projections_fused_qkv_matches_three_products_and_fp32_reference():
-    """LlamaTernaryAttention: one fused q|k|v product against the reference's three separate products
-    (ternaryLLM_GPU/TernaryLLM/TernaryAttn.py:73-75) and against plain fp32 PyTorch on the dense weights;
-    decode with a (k, v) cache and a causal multi-token call.  Tolerance 2e-2 of the largest output (fp16 rounding
-    between the stages)."""
-    import torch.nn.functional as F
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_peer_allreduce_with_a_stand_in_peer(dtype):
+    """Rank 0 of a two-rank communicator on one GPU.  The peer is a pair of buffers of this process: the kernel pushes
+    rank 0's rows into them (checked), and finds rank 1's rows and flag already in its own receive buffer, where the
+    host put them -- the data path of a real peer without a second kernel that this one would have to wait for.
+    x += p0 + p1 in fp32, rounded once; h = RMSNorm(x) * weight.  Three calls in a row: the epochs and the two buffer
+    sets advance."""
+    import ctypes as C
 
-    from ternaryllm_b200 import LlamaTernaryAttention, TernaryConfig
+    from ternaryllm_b200 import _lib
 
+    L = _lib.lib()
     dev = torch.device("cuda", 0)
-    cfg = TernaryConfig(hidden_size=1024, intermediate_size=2816, num_attention_heads=8, num_key_value_heads=2, sparsity=0.6)
-    g = torch.Generator().manual_seed(3)
-    attn = LlamaTernaryAttention(cfg, layer_idx=0, scales=(0.03125,) * 4, generator=g)
-    assert attn.fused_qkv
-    hd, hq, hkv = cfg.head_dim, 8, 2
-    x = torch.randn((2, 5, 1024), generator=g).to(dev, torch.float16)
-    y, _, (k, v) = attn(x, use_cache=True)
-    attn.fused_qkv = False
-    y3, _, _ = attn(x, use_cache=True)
-    attn.fused_qkv = True
-    assert (y.float() - y3.float()).abs().max() <= 2e-3 * y3.float().abs().max()
+    rows, hidden, world = 3, 1024, 2
+    h = _comm(world, 0, rows, hidden)
+    recv, flags, rb, fb = C.c_void_p(), C.c_void_p(), C.c_int64(), C.c_int64()
+    _lib.check(L.tllm_comm_buffers(h, C.byref(recv), C.byref(flags), C.byref(rb), C.byref(fb)))
+    assert rb.value == 2 * world * rows * hidden * 4 and fb.value == 2 * world * rows * 4
+    peer_recv = torch.zeros(rb.value // 4, dtype=torch.float32, device=dev)
+    peer_flags = torch.zeros(fb.value // 4, dtype=torch.int32, device=dev)
+    _lib.check(L.tllm_comm_attach(h, 1, peer_recv.data_ptr(), peer_flags.data_ptr()))
+    g = torch.Generator(device="cpu").manual_seed(1)
+    x = torch.randn((rows, hidden), generator=g).to(dev, dtype)
+    wgt = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dev, dtype)
+    for call in range(3):
+        epoch, st = call + 1, (call + 1) & 1
+        p0 = torch.randn((rows, hidden), generator=g).to(dev)
+        p1 = torch.randn((rows, hidden), generator=g).to(dev)
+        # the peer's part: its rows into slot [set][source 1] of rank 0's receive buffer, then its flags
+        _copy(recv.value + ((st * world + 1) * rows) * hidden * 4, p1.contiguous())
+        _copy(flags.value + ((st * world + 1) * rows) * 4, torch.full((rows,), epoch, dtype=torch.int32, device=dev))
+        want_x = (x.float() + (p0 + p1)).to(dtype)
+        hh = torch.empty_like(x)
+        _lib.check(L.tllm_allreduce_add_rmsnorm(h, p0.data_ptr(), x.data_ptr(), wgt.data_ptr(), hh.data_ptr(), _lib.torch_dtype_code(dtype), rows,
+                                                1e-6, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        _lib.check(L.tllm_comm_check(h))
+        assert torch.equal(x, want_x), call
+        v = want_x.float()
+        want_h = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * wgt.float()
+        assert (hh.float() - want_h).abs().max().item() <= 2e-2 * want_h.abs().max().item()
+        # what rank 0 pushed to its peer: its rows in slot [set][src = 0], and the flags
+        got = peer_recv[((st * world + 0) * rows) * hidden:((st * world + 0) * rows + rows) * hidden].view(rows, hidden)
+        assert torch.equal(got, p0)
+        assert torch.all(peer_flags[(st * world + 0) * rows:(st * world + 0) * rows + rows] == epoch)
+    L.tllm_comm_destroy(h)
 
-    W = {n: getattr(attn, n).ternary_weight.to(dev, torch.float32) * 0.03125 for n in ("q_proj", "k_proj", "v_proj", "o_proj")}
 
-    def ref(xf, past=None, causal=True):
-        b, t, _ = xf.shape
-        q = (xf @ W["q_proj"]).view(b, t, hq, hd).transpose(1, 2)
-        kk = (xf @ W["k_proj"]).view(b, t, hkv, hd).transpose(1, 2)
-        vv = (xf @ W["v_proj"]).view(b, t, hkv, hd).transpose(1, 2)
-        if past is not None:
-            kk, vv = torch.cat([past[0], kk], 2), torch.cat([past[1], vv], 2)
-        o = F.scaled_dot_product_attention(q, kk.repeat_interleave(hq // hkv, 1), vv.repeat_interleave(hq // hkv, 1), is_causal=causal and t > 1)
-        return o.transpose(1, 2).reshape(b, t, hq * hd) @ W["o_proj"], (kk, vv)
+def _copy(dst_ptr, src):
+    """device-to-device copy of a tensor to a raw device address"""
+    from cuda.bindings import runtime as rt
 
-    want, (kr, vr) = ref(x.float())
-    assert (y.float() - want).abs().max() <= 2e-2 * want.abs().max()
-    # one more token on top of the cache
-    x1 = torch.randn((2, 1, 1024), generator=g).to(dev, torch.float16)
-    y1, _, _ = attn(x1, past_key_value=(k, v), use_cache=True)
-    want1, _ = ref(x1.float(), past=(kr, vr), causal=False)
-    assert (y1.float() - want1).abs().max() <= 2e-2 * want1.abs().max()
+    (err,) = rt.cudaMemcpy(dst_ptr, src.data_ptr(), src.numel() * src.element_size(), rt.cudaMemcpyKind.cudaMemcpyDeviceToDevice)
+    assert int(err) == 0, err
 
 
 @pytest.mark.gpu
-def test_add_rms_norm_matches_pytorch():
-    """tllm_add_rmsnorm against the same arithmetic in PyTorch (fp32 sums, one rounding of the stream, one of the
-    normalised output): the stream must be identical, the output within one unit in the last place."""
-    from ternaryllm_b200.tensor_parallel import add_rms_norm
+def test_peer_allreduce_gives_up_when_a_flag_never_comes():
+    """The peer's flag is never set: after the wait limit (set to 20 ms) the kernel stops waiting, finishes and writes
+    the status word; the host reads it as an error, and the GPU keeps working."""
+    import ctypes as C
 
+    from ternaryllm_b200 import _lib
+
+    L = _lib.lib()
     dev = torch.device("cuda", 0)
-    g = torch.Generator().manual_seed(8)
-    for dtype, ulp in ((torch.float32, 2.0 ** -22), (torch.float16, 2.0 ** -10), (torch.bfloat16, 2.0 ** -7)):
-        for rows, hidden in ((1, 8192), (5, 1000), (64, 4096)):
-            x = torch.randn((rows, hidden), generator=g).to(dev, dtype)
-            d = torch.randn((rows, hidden), generator=g).to(dev, dtype)
-            w = (torch.rand((hidden,), generator=g) + 0.5).to(dev, dtype)
-            x2 = x.clone()
-            h = add_rms_norm(x2, d, weight=w)
-            xr = (x.float() + d.float()).to(dtype)
-            assert torch.equal(x2, xr)
-            hr = xr.float() * torch.rsqrt(xr.float().pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
-            assert ((h.float() - hr).abs() <= ulp * hr.abs() + 1e-6).all()
-            x3 = x.clone()
-            h0 = add_rms_norm(x3, None)
-            assert torch.equal(x3, x)
-            h0r = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)
-            assert ((h0.float() - h0r).abs() <= ulp * h0r.abs() + 1e-6).all()
+    rows, hidden = 2, 512
+    h = _comm(2, 0, rows, hidden)
+    rb, fb = C.c_int64(), C.c_int64()
+    _lib.check(L.tllm_comm_buffers(h, None, None, C.byref(rb), C.byref(fb)))
+    peer_recv = torch.zeros(rb.value // 4, dtype=torch.float32, device=dev)
+    peer_flags = torch.zeros(fb.value // 4, dtype=torch.int32, device=dev)
+    _lib.check(L.tllm_comm_attach(h, 1, peer_recv.data_ptr(), peer_flags.data_ptr()))
+    _lib.check(L.tllm_comm_set_wait_limit(h, 20.0))
+    x = torch.zeros((rows, hidden), dtype=torch.bfloat16, device=dev)
+    p0 = torch.ones((rows, hidden), dtype=torch.float32, device=dev)
+    hh = torch.empty_like(x)
+    _lib.check(L.tllm_allreduce_add_rmsnorm(h, p0.data_ptr(), x.data_ptr(), None, hh.data_ptr(), _lib.BF16, rows, 1e-6,
+                                            torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert L.tllm_comm_check(h) == -3 and b"never arrived" in L.tllm_last_error()
+    assert L.tllm_comm_check(h) == 0                   # reported once
+    assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0     # the context is alive
+    L.tllm_comm_destroy(h)
+    # an unconnected communicator is refused on the host
+    h2 = _comm(2, 1, rows, hidden)
+    assert L.tllm_allreduce_add_rmsnorm(h2, p0.data_ptr(), x.data_ptr(), None, hh.data_ptr(), _lib.BF16, rows, 1e-6, None) == -1
+    L.tllm_comm_destroy(h2)
