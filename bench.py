@@ -166,10 +166,26 @@ def spmv_records(torch, device, peak_hbm, quick=False):
     rng = np.random.default_rng(12345)
     out = {"sweep": [], "other_configs": []}
 
-    def product(K, N, S, M, dtype=torch.float16, seed0=1000, check=True):
-        """R distinct weights of one shape replayed from a graph; returns a record"""
+    KERNELS = {"gather": "gather (index lists)", "mma": "tensor core (two-bit tiles)", "nibble": "decode tensor core (four-bit planes by TMA)"}
+
+    def pin(which):
+        """auto = the library's cost model; gather / nibble = that kernel for every call it can take"""
+        L.tllm_set_mma_min_rows(0 if which == "gather" else -1)
+        L.tllm_set_nibble_max_rows({"auto": -1, "gather": 0, "nibble": 64}[which])
+
+    def counters():
+        return L.tllm_mma_launch_count(), L.tllm_nibble_launch_count()
+
+    def ran_since(c0):
+        m1, n1 = counters()
+        names = ([KERNELS["mma"]] if m1 > c0[0] else []) + ([KERNELS["nibble"]] if n1 > c0[1] else [])
+        return " + ".join(names) if names else KERNELS["gather"]
+
+    def product(K, N, S, M, dtype=torch.float16, seed0=1000, check=True, pins=("auto",)):
+        """R distinct weights of one shape replayed from a graph, once per kernel choice in `pins`; returns the record of
+        pins[0] with the others' times under "by_kernel" """
         e = torch.empty((), dtype=dtype).element_size()
-        bytes_one = int(K * N * (1 - S)) * 1.1 + 1
+        bytes_one = min(int(K * N * (1 - S)) * 1.1 + 1, K * N / 2)     # the fewest bytes any kernel reads per weight
         R = min(48, max(3, int(-(-3 * L2_BYTES // bytes_one)) + 1))     # small weights stay (and are marked) L2-resident
         scales = [float(np.float16(v)) for v in rng.uniform(0.01, 0.05, R)]
         packed, nnzs, w0 = [], [], None
@@ -183,45 +199,57 @@ def spmv_records(torch, device, peak_hbm, quick=False):
         info = packed[0].info
         X = torch.tensor(rng.standard_normal((M, K)), dtype=dtype, device=device)
         Y = [torch.empty((M, N), dtype=dtype, device=device) for _ in range(R)]
-        m0 = L.tllm_mma_launch_count()
+        balg = algorithmic_bytes(nnz, K, N, M, e)
 
         def step():
             for i in range(R):
                 packed[i].matmul(X, out=Y[i])
 
-        step()
-        torch.cuda.synchronize()
-        tensor = L.tllm_mma_launch_count() > m0
-        err = None
-        if check:
-            ref = (X.double() @ torch.tensor(w0, device=device).double()) * scales[0]
-            err = float((Y[0].double() - ref).abs().max() / ref.abs().max())
-            if not err <= 1e-3 + 2.0 ** -8:
-                raise SystemExit(f"benchmark output differs from the dense product (rel err {err}) at {K}x{N} S={S} M={M}")
-        g = capture(torch, step)
-        us, reps = timed_us(torch, g.replay, 0.05 if quick else 0.2)
-        us /= R
-        for p in packed:
-            p.check()
-        balg = algorithmic_bytes(nnz, K, N, M, e)
-        bphys = (info["bit_tile_bytes"] if tensor else info["stream_bytes"] + info["meta_bytes"]) + e * M * (K + N)
-        rec = {"K": K, "N": N, "zeros": S, "rows": M, "kernel": "tensor-core" if tensor else "gather", "us_per_launch": us,
-               "algorithmic_GBps": balg / us / 1e3, "frac": balg / us / 1e3 / peak_hbm, "physical_bytes": int(bphys),
-               "frac_physical": bphys / us / 1e3 / peak_hbm, "GOPs": M * nnz / us / 1e3, "weights_in_rotation": R, "rotation_exceeds_l2": bool(R * bytes_one > 2 * L2_BYTES),
-               "graph_replays_timed": reps, "check_rel_err": err, "algorithmic_bytes": balg, "nnz": nnz,
-               "pack": {k: info[k] for k in ("tile_rows", "tiles", "col_blocks", "k_splits", "num_ctas", "units")}}
+        recs = []
+        for which in pins:
+            pin(which)
+            m0, n0 = L.tllm_mma_launch_count(), L.tllm_nibble_launch_count()
+            step()
+            torch.cuda.synchronize()
+            kern = "mma" if L.tllm_mma_launch_count() > m0 else ("nibble" if L.tllm_nibble_launch_count() > n0 else "gather")
+            err = None
+            if check:
+                ref = (X.double() @ torch.tensor(w0, device=device).double()) * scales[0]
+                err = float((Y[0].double() - ref).abs().max() / ref.abs().max())
+                if not err <= 1e-3 + 2.0 ** -8:
+                    raise SystemExit(f"benchmark output differs from the dense product (rel err {err}) at {K}x{N} S={S} M={M} ({which})")
+            g = capture(torch, step)
+            us, reps = timed_us(torch, g.replay, 0.05 if quick else 0.2)
+            us /= R
+            for p in packed:
+                p.check()
+            wbytes = {"mma": info["bit_tile_bytes"], "nibble": info["nibble_bytes"], "gather": info["stream_bytes"] + info["meta_bytes"]}[kern]
+            bphys = wbytes + e * M * (K + N)
+            recs.append({"K": K, "N": N, "zeros": S, "rows": M, "choice": which, "kernel": KERNELS[kern], "us_per_launch": us,
+                         "algorithmic_GBps": balg / us / 1e3, "frac": balg / us / 1e3 / peak_hbm, "physical_bytes": int(bphys),
+                         "frac_physical": bphys / us / 1e3 / peak_hbm, "GOPs": M * nnz / us / 1e3, "weights_in_rotation": R,
+                         "rotation_exceeds_l2": bool(R * bytes_one > 2 * L2_BYTES), "graph_replays_timed": reps, "check_rel_err": err,
+                         "algorithmic_bytes": balg, "nnz": nnz})
+        pin("auto")
+        rec = recs[0]
+        rec["pack"] = {k: info[k] for k in ("tile_rows", "tiles", "col_blocks", "k_splits", "num_ctas", "units", "stream_bytes", "meta_bytes",
+                                             "nibble_bytes", "bit_tile_bytes")}
+        if len(recs) > 1:
+            rec["by_kernel"] = [{k: r[k] for k in ("choice", "kernel", "us_per_launch", "algorithmic_GBps", "frac", "physical_bytes", "frac_physical")}
+                                for r in recs[1:]]
         for p in packed:
             p.close()
         return rec
 
-    out["headline"] = product(K_IN, N_OUT, 0.75, 1)
+    both = ("auto", "gather", "nibble")
+    out["headline"] = product(K_IN, N_OUT, 0.75, 1, pins=both)
     for S in ((0.5, 0.9) if quick else (0.5, 0.6, 0.7, 0.8, 0.9)):
-        out["sweep"].append(product(K_IN, N_OUT, S, 1, seed0=2000 + int(S * 100)))
+        out["sweep"].append(product(K_IN, N_OUT, S, 1, seed0=2000 + int(S * 100), pins=both))
     if quick:
         return out
     for M in (4, 16):
-        out["other_configs"].append(dict(product(K_IN, N_OUT, 0.75, M, seed0=1000), workload=f"C2 up-projection shape, {M} rows fp16"))
-    out["other_configs"].append(dict(product(8192, 28672, 0.5, 1, dtype=torch.bfloat16, seed0=3000), workload="70B up-projection shape, 1 row bf16"))
+        out["other_configs"].append(dict(product(K_IN, N_OUT, 0.75, M, seed0=1000, pins=both if M == 4 else ("auto",)), workload=f"C2 up-projection shape, {M} rows fp16"))
+    out["other_configs"].append(dict(product(8192, 28672, 0.5, 1, dtype=torch.bfloat16, seed0=3000, pins=both), workload="70B up-projection shape, 1 row bf16"))
     # C1: the reference's own CPU case, M = 8, K = N = 2048, fp32 N(0,1), 50 % zeros
     out["other_configs"].append(dict(product(2048, 2048, 0.5, 8, dtype=torch.float32, seed0=0), workload="C1: X[8,2048] fp32, W[2048,2048] 50% zeros"))
     # C3: fused MLP 4096 -> 11008 -> 4096, 60 % zeros, fp16 (two launches per block: gate|up with SiLU*mul, then down)
@@ -240,7 +268,7 @@ def spmv_records(torch, device, peak_hbm, quick=False):
         X = torch.tensor(mrng.standard_normal((M, hidden)), dtype=torch.float16, device=device)
         Y = torch.empty((M, hidden), dtype=torch.float16, device=device)
         H = torch.empty((M, inter), dtype=torch.float16, device=device)
-        m0 = L.tllm_mma_launch_count()
+        c0 = counters()
         mlps[0].forward(X, out=Y, h=H)
         torch.cuda.synchronize()
         (wg, wu, wd), (sg, su, sd) = wsets[0]
@@ -259,7 +287,7 @@ def spmv_records(torch, device, peak_hbm, quick=False):
         us /= len(mlps)
         balg = balg_w + 2 * M * 2 * hidden
         out["other_configs"].append({"workload": f"C3: MLP block {hidden}->{inter}->{hidden}, 60% zeros, {M} rows fp16 (two launches)",
-                                     "kernel": "tensor-core" if L.tllm_mma_launch_count() > m0 else "gather", "us_per_block": us,
+                                     "kernel": ran_since(c0), "us_per_block": us,
                                      "algorithmic_GBps": balg / us / 1e3, "frac": balg / us / 1e3 / peak_hbm, "check_rel_err": err})
     for m in mlps:
         m.close()
@@ -271,7 +299,7 @@ def spmv_records(torch, device, peak_hbm, quick=False):
         wq = PackedWeight.from_dense(w, scale=0.02, device=device)
         X = torch.randn((Mp, Kp), device=device).to(torch.bfloat16)
         Y = torch.empty((Mp, Np), dtype=torch.bfloat16, device=device)
-        m0 = L.tllm_mma_launch_count()
+        c0 = counters()
         wq.matmul(X, out=Y)
         ref = (X[:128].double() @ torch.tensor(w, device=device).double()) * 0.02
         err = float((Y[:128].double() - ref).abs().max() / ref.abs().max())
@@ -280,7 +308,7 @@ def spmv_records(torch, device, peak_hbm, quick=False):
         us, _ = timed_us(torch, lambda: wq.matmul(X, out=Y), 0.1)
         tf = 2.0 * Mp * Kp * Np / us / 1e6
         out["other_configs"].append({"workload": f"C4: {name} prefill, X[{Mp},{Kp}] bf16, W[{Kp},{Np}] 50% zeros",
-                                     "kernel": "tensor-core" if L.tllm_mma_launch_count() > m0 else "gather", "us_per_launch": us,
+                                     "kernel": ran_since(c0), "us_per_launch": us,
                                      "dense_equivalent_TFLOPs": tf, "frac_of_bf16_peak": tf / peak_tc, "bf16_peak_TFLOPs": peak_tc,
                                      "peak_source": kind, "check_rel_err": err})
         wq.close()
@@ -356,10 +384,11 @@ def decoder_bench(torch, dist, world, rank, device, steps, warmup, sparsities, b
                     x, pending = layers[i % nsets](x, pending)
                 result["y"] = layers[0].finish(x, pending)
 
-            n0, m0 = L.tllm_launch_count(), L.tllm_mma_launch_count()
+            n0, m0, d0 = L.tllm_launch_count(), L.tllm_mma_launch_count(), L.tllm_nibble_launch_count()
             step()
             torch.cuda.synchronize()
             launches, tensor_launches = L.tllm_launch_count() - n0, L.tllm_mma_launch_count() - m0
+            decode_tc_launches = L.tllm_nibble_launch_count() - d0
             assert torch.isfinite(result["y"].float()).all()
             graph = capture(torch, step)
             y = result["y"]                           # the tensor the captured step writes
@@ -396,6 +425,7 @@ def decoder_bench(torch, dist, world, rank, device, steps, warmup, sparsities, b
                 ms, dt_e2e = float(t[0]), float(t[1])
             rec = {"zeros": S, "batch": batch, "tokens_per_s": batch / (ms * 1e-3), "ms_per_step": ms, "steps": nsteps,
                    "e2e_tokens_per_s": batch / dt_e2e, "launches_per_step": int(launches), "tensor_core_launches_per_step": int(tensor_launches),
+                   "decode_tensor_core_launches_per_step": int(decode_tc_launches),
                    "weight_sets": nsets, "algorithmic_weight_GBps_per_rank": alg_local / (ms * 1e-3) / 1e9, "parity_rel_err": parity,
                    "h2d_bytes_per_step": batch * d["hidden"] * 2, "d2h_bytes_per_step": batch * d["hidden"] * 2}
             if headline is None:
@@ -592,7 +622,9 @@ def main():
             h = spmv["headline"]
             line["roofline"] = {"bound": "hbm", "achieved": h["algorithmic_GBps"], "peak": peak, "unit": "GB/s", "frac": h["frac"],
                                 "frac_physical": h["frac_physical"], "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
-                                "kernel": "bstream_spmm_kernel<float,1>", "us_per_launch": h["us_per_launch"],
+                                "kernel": "nibble_spmm_kernel" if h["kernel"].startswith("decode") else "bstream_spmm_kernel<float,1>",
+                                "kernel_choice": "the library's cost model (both kernels' times are under spmv.headline.by_kernel)",
+                                "us_per_launch": h["us_per_launch"],
                                 "workload": f"decode product x[1,{K_IN}] fp16, W[{K_IN},{N_OUT}] 75% zeros, {h['weights_in_rotation']} weights in rotation (larger than L2)",
                                 "algorithmic_bytes_per_launch": h["algorithmic_bytes"], "physical_bytes_per_launch": h["physical_bytes"],
                                 "traffic": NCU_TRAFFIC["bytes"], "traffic_source": NCU_TRAFFIC["source"]}

@@ -51,6 +51,16 @@ int64_t tllm_mma_launch_count(void);
  *   rows > 0  the tensor-core kernel from that many activation rows on
  * Process-wide; returns the previous setting.  The environment variable TLLM_MMA_MIN_ROWS sets the initial one. */
 int tllm_set_mma_min_rows(int rows);
+/* Which kernel takes a call of a few rows (fp16 / bf16: up to 4, fp32: up to 2 rows per launch; more rows take several
+ * launches): the gather kernel on the index lists, or the decode tensor-core kernel that streams the four-bit copy of W
+ * by TMA (half a byte per entry whatever the sparsity; the gather kernel's cost grows with the non-zeros).
+ *   rows < 0  decide per call from a measured cost model of the two (default)
+ *   rows = 0  never the decode tensor-core kernel
+ *   rows > 0  always, for calls of up to that many rows
+ * tllm_set_mma_min_rows(0) switches this kernel off as well.  Process-wide; returns the previous setting. */
+int tllm_set_nibble_max_rows(int rows);
+/* launches of the decode tensor-core kernel so far in this process */
+int64_t tllm_nibble_launch_count(void);
 
 /* --------------------------------------------------------------------------------------------------
  * Host-side packers: the four callables of the reference's `ter_spmm` extension module
@@ -114,9 +124,11 @@ typedef struct tllm_pack_opts {
     int reserved0;        /* must be 0 */
     int max_rows;         /* rows of one gather launch, 1..4 (the split-K scratch is sized for it); 0 = 4 */
     int k_splits;         /* thread blocks that share one column range along K; 0 = choose (1 = no split-K scratch) */
-    int no_bit_tiles;     /* 1 = do not keep the dense two-bit copy of W that the tensor-core kernel reads (every call
-                             then runs the gather kernel); 0 = keep it (columns*inners/4 bytes) */
-    int reserved[2];
+    int no_bit_tiles;     /* 1 = do not keep the dense two-bit copy of W that the batched tensor-core kernel reads
+                             (columns*inners/4 bytes); 0 = keep it */
+    int no_nibbles;       /* 1 = do not keep the four-bit transposed copy of W that the decode tensor-core kernel streams
+                             (columns*inners/2 bytes); 0 = keep it.  With neither copy every call runs the gather kernel. */
+    int reserved[1];
 } tllm_pack_opts;
 
 typedef struct tllm_weight_info {
@@ -128,7 +140,8 @@ typedef struct tllm_weight_info {
     int64_t meta_bytes;        /* block tables as stored */
     int64_t scratch_bytes;     /* split-K partial sums + counters owned by the handle */
     int64_t algorithmic_bytes; /* 2*nnz + 16*columns*ceil(inners/512): the reference layout's weight bytes */
-    int64_t bit_tile_bytes;    /* dense two-bit copy read by the tensor-core kernel (0 if not kept) */
+    int64_t bit_tile_bytes;    /* dense two-bit copy read by the batched tensor-core kernel (0 if not kept) */
+    int64_t nibble_bytes;      /* four-bit transposed copy streamed by the decode tensor-core kernel (0 if not kept) */
     float scale;
 } tllm_weight_info;
 
@@ -247,9 +260,18 @@ int tllm_mlp_forward(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y,
  * tensor-parallel layer hands to the all-reduce). */
 int tllm_mlp_forward_ex(tllm_mlp* m, const void* X, int x_dtype, int rows, void* Y, int y_dtype, void* H, void* stream);
 /* Same with HOST buffers and the reference's in-place convention (TernaryMLP<T>::forward overwrites its input with the
- * block's output, LlamaModel.hpp:343-452): X [rows][hidden] row-major is copied to the device, the block runs, the
- * result is copied back over X; H (host, rows*intermediate values, may be NULL) receives silu(gate)*up. Synchronises. */
-int tllm_mlp_forward_host(tllm_mlp* m, void* X, int x_dtype, int rows, void* H);
+ * block's output, LlamaModel.hpp:165-270 and :343-452): X ([rows][hidden] for TLLM_ROW_MAJOR, [hidden][rows] for
+ * TLLM_COL_MAJOR as the reference's colMajor kernels take it) is copied to the device, the block runs, the result is
+ * copied back over X in the same layout; H (host, rows*intermediate values in that layout, may be NULL) receives
+ * silu(gate)*up. Synchronises. */
+int tllm_mlp_forward_host(tllm_mlp* m, void* X, int x_dtype, int x_layout, int rows, void* H);
+/* The block from three weights in one of the reference's single-array CPU formats (kinds 1..5 of
+ * tllm_weight_create_cpu_format; gate and up are [hidden] x [intermediate], down is [intermediate] x [hidden]): what
+ * TernaryMLP<T> keeps in WG_/WU_/WD_metadata and _rowindex (LlamaModel.hpp:95-100, :276-281). Scales are 1. */
+int tllm_mlp_create_cpu_format(int kind, int group, int chunk, int ri32, const int32_t* meta_gate, const void* ri_gate,
+                               const int32_t* meta_up, const void* ri_up, const int32_t* meta_down,
+                               const void* ri_down, int hidden, int intermediate, const tllm_pack_opts* opts,
+                               tllm_mlp** out);
 int tllm_mlp_get_info(const tllm_mlp* m, tllm_weight_info* gate_up, tllm_weight_info* down);
 
 /* Exact SiLU(x)*y epilogue on its own (Naive_SiLU_Dot, ternaryLLM_CPU/src/initData.hpp:204-210):

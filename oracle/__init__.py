@@ -42,6 +42,13 @@ def lib():
     return _lib
 
 
+def reference_root() -> str:
+    """Where a checkout of the reference project is looked for: $TLLM_REFERENCE_ROOT, else a directory named
+    `reference` beside this repository.  It need not exist; callers test for the sources they want."""
+    env = os.environ.get("TLLM_REFERENCE_ROOT")
+    return env if env else os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 def have_ref() -> bool:
     return os.path.exists(_REF)
 

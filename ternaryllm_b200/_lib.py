@@ -18,13 +18,13 @@ ROW_MAJOR, COL_MAJOR = 0, 1
 
 class PackOpts(C.Structure):
     _fields_ = [("tile_rows", C.c_int), ("num_ctas", C.c_int), ("reserved0", C.c_int), ("max_rows", C.c_int),
-                ("k_splits", C.c_int), ("no_bit_tiles", C.c_int), ("reserved", C.c_int * 2)]
+                ("k_splits", C.c_int), ("no_bit_tiles", C.c_int), ("no_nibbles", C.c_int), ("reserved", C.c_int * 1)]
 
 
 class WeightInfo(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("inners", "columns", "tile_rows", "tiles", "col_blocks", "k_splits",
                                        "tiles_per_cta", "num_ctas", "units", "max_rows")] + [
-        (n, C.c_int64) for n in ("nnz", "stream_bytes", "meta_bytes", "scratch_bytes", "algorithmic_bytes", "bit_tile_bytes")] + [
+        (n, C.c_int64) for n in ("nnz", "stream_bytes", "meta_bytes", "scratch_bytes", "algorithmic_bytes", "bit_tile_bytes", "nibble_bytes")] + [
         ("scale", C.c_float)]
 
     def as_dict(self):
@@ -39,6 +39,8 @@ SIGNATURES = {
     "tllm_launch_count": (_L, []),
     "tllm_mma_launch_count": (_L, []),
     "tllm_set_mma_min_rows": (_I, [_I]),
+    "tllm_set_nibble_max_rows": (_I, [_I]),
+    "tllm_nibble_launch_count": (_L, []),
     "tllm_count_nnz": (_I, [_P, _I, _I, _P, _P]),
     "tllm_convert_to_ter_csc": (_I, [_P, _I, _I, _P, _P, _P, _P]),
     "tllm_convert_to_ter_tiled_csc": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
@@ -66,7 +68,8 @@ SIGNATURES = {
     "tllm_mlp_destroy": (_I, [_P]),
     "tllm_mlp_forward": (_I, [_P, _P, _I, _I, _P, _P, _P]),
     "tllm_mlp_forward_ex": (_I, [_P, _P, _I, _I, _P, _I, _P, _P]),
-    "tllm_mlp_forward_host": (_I, [_P, _P, _I, _I, _P]),
+    "tllm_mlp_forward_host": (_I, [_P, _P, _I, _I, _I, _P]),
+    "tllm_mlp_create_cpu_format": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P]),
     "tllm_mlp_get_info": (_I, [_P, _P, _P]),
     "tllm_silu_mul": (_I, [_P, _P, _I, _L, _P]),
     "tllm_add_rmsnorm": (_I, [_P, _P, _P, _P, _I, _I, _I, _F, _P]),

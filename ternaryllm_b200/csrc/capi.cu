@@ -13,6 +13,8 @@
 #include "bstream_kernel.cuh"
 #include "kernels.cuh"
 #include "mma_kernel.cuh"
+#include "nibble_format.h"
+#include "nibble_kernel.cuh"
 #include "util.h"
 
 namespace tllm {
@@ -61,19 +63,35 @@ static int mm_min_rows() {
     }
     return v;
 }
-// Cost model measured on B200 (CUDA-graph replays, weights streamed from HBM), microseconds: a gather launch of up
-// to four rows costs about GATHER_FIXED + nnz * g(rows padded to 1, 2, 4), more rows take ceil(rows / 4) launches;
-// the tensor-core kernel about 9 + 0.21e-6 per matrix entry whatever the row count up to 64.  One row always takes
-// the gather kernel; the model decides from two rows on.
-static const double GATHER_FIXED_US = 3.0;
-static const double GATHER_PS_PER_NNZ[3] = {0.25, 0.40, 0.75};
-static bool mm_model_prefers_tensor(int64_t nnz, int64_t entries, int rows) {
-    if (rows < 2) return false;
+// Cost model measured on B200 (CUDA-graph replays of back-to-back products, weights streamed from HBM), microseconds:
+// a gather launch of up to four rows costs about GATHER_FIXED + nnz * g(rows padded to 1, 2, 4), more rows take
+// ceil(rows / 4) launches; the batched tensor-core kernel about 9.8 + 0.205e-6 per matrix entry whatever the row count
+// up to 64; the decode tensor-core kernel is modelled below.  Every call goes to the kernel the model finds fastest.
+static const double GATHER_FIXED_US = 2.9;
+static const double GATHER_PS_PER_NNZ[3] = {0.48, 0.68, 1.35};
+// The decode tensor-core kernel: -1 = cost model, 0 = never, n > 0 = always for calls of up to n rows.
+static std::atomic<int> g_nb_max_rows{-1};
+static std::atomic<int64_t> g_nb_launches{0};
+#ifdef NB_DEBUG
+static int g_nb_debug_tx = 0;   // diagnostic builds only: bytes a weight tile's copy is expected to report
+static int g_nb_debug_stages = 0, g_nb_debug_flags = 0, g_nb_debug_cg = 0;
+#endif
+// one launch of the decode tensor-core kernel: half a byte per entry at 5.2 TB/s around 6.7 us of start-up (building B
+// once the preceding kernel has finished) and hand-over between blocks, 2.2 us more for every further row
+static const double NB_FIXED_US = 6.7, NB_ROW_US = 2.2, NB_US_PER_ENTRY = 0.5 / 5.2e6;
+static double gather_model_us(int64_t nnz, int rows) {
     const int full = rows / 4, tail = rows % 4;
     const int idx = tail <= 1 ? 0 : (tail == 2 ? 1 : 2);
-    const double t_gather = full * (GATHER_FIXED_US + nnz * GATHER_PS_PER_NNZ[2] * 1e-6) + (tail ? GATHER_FIXED_US + nnz * GATHER_PS_PER_NNZ[idx] * 1e-6 : 0.0);
-    const double t_tensor = 9.0 + entries * 0.21e-6 * (rows <= 64 ? 1.0 : rows / 64.0);
-    return t_tensor < t_gather;
+    return full * (GATHER_FIXED_US + nnz * GATHER_PS_PER_NNZ[2] * 1e-6) + (tail ? GATHER_FIXED_US + nnz * GATHER_PS_PER_NNZ[idx] * 1e-6 : 0.0);
+}
+static double nibble_model_us(int64_t entries, int rows, int rows_per_launch) {
+    const int launches = (rows + rows_per_launch - 1) / rows_per_launch;
+    return launches * (NB_FIXED_US + entries * NB_US_PER_ENTRY) + (rows - launches) * NB_ROW_US;
+}
+static double mm_model_us(int64_t entries, int rows) { return 9.8 + entries * 0.205e-6 * (rows <= 64 ? 1.0 : rows / 64.0); }
+static bool mm_model_prefers_tensor(int64_t nnz, int64_t entries, int rows) {
+    if (rows < 2) return false;
+    return mm_model_us(entries, rows) < gather_model_us(nnz, rows);
 }
 
 }  // namespace tllm
@@ -107,6 +125,14 @@ struct tllm_weight {
     unsigned int* d_mm_counters = nullptr;
     size_t bits_bytes = 0;
     int mm_n_tiles = 0, mm_kb = 0, mm_grid = 0;
+    // decode tensor-core kernel: transposed four-bit copy of W, its tensor map, schedule and hand-over scratch
+    uint8_t* d_nib = nullptr;
+    size_t nib_bytes = 0;
+    CUtensorMap nib_map;
+    int nb_kb = 0, nb_kbs = 0, nb_splits = 0, nb_tiles = 0, nb_gj = 0;
+    float* d_nb_partial = nullptr;
+    unsigned int* d_nb_counters = nullptr;
+    uint32_t* d_nb_sched = nullptr;
     // the activation tensor map of the last tensor-core launch (encoding one costs more than a short launch)
     CUtensorMap tmap;
     const void* tmap_x = nullptr;
@@ -292,6 +318,150 @@ int run_mm(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void*
     return TLLM_OK;
 }
 
+// ---- decode tensor-core path ---------------------------------------------------------------------------------
+int nb_rows_per_launch(int x_dtype) { return x_dtype == TLLM_F32 ? NB_ROWS / 8 : NB_ROWS / 4; }
+
+// true when the decode tensor-core kernel can and should take this call
+bool nb_usable(const tllm_weight* w, int x_dtype, int x_layout, int rows) {
+    if (!w->d_nib || (x_dtype != TLLM_F16 && x_dtype != TLLM_BF16 && x_dtype != TLLM_F32) || x_layout != TLLM_ROW_MAJOR) return false;
+    if (mm_min_rows() == 0) return false;
+    const int thr = g_nb_max_rows.load(std::memory_order_relaxed);
+    if (thr == 0) return false;
+    if (thr > 0) return rows <= thr;
+    const int64_t entries = (int64_t)w->lay.inners * w->lay.columns;
+    return nibble_model_us(entries, rows, nb_rows_per_launch(x_dtype)) < gather_model_us(w->lay.nnz, rows);
+}
+
+int upload_nibbles(tllm_weight* w, const int8_t* dense, int inners, int columns, int sms) {
+    if (tensor_map_encoder() == nullptr) return TLLM_OK;      // no driver entry point: the handle simply has no such copy
+    NbHostImage img;
+    nb_pack_dense(dense, inners, columns, &img);
+    w->nib_bytes = img.codes.size();
+    CU_TRY(cudaMalloc(&w->d_nib, w->nib_bytes));
+    CU_TRY(cudaMemcpy(w->d_nib, img.codes.data(), w->nib_bytes, cudaMemcpyHostToDevice));
+    const cuuint64_t dims[2] = {(cuuint64_t)img.k_pad, (cuuint64_t)img.n_pad};
+    const cuuint64_t strides[1] = {(cuuint64_t)img.k_pad / 2};
+    const cuuint32_t box[2] = {NB_TILE_K, NB_TILE_N};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult cr = tensor_map_encoder()(&w->nib_map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, w->d_nib, dims, strides, box, estr,
+                                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(TLLM_ERR_CUDA, "cuTensorMapEncodeTiled (four-bit weight planes) failed with code %d", (int)cr);
+    // K ranges of at most NB_MAX_KBS blocks, all ranges the same number of thread blocks, never more blocks in a range
+    // than its shortest list of (tile, K block) units
+    w->nb_kb = img.k_pad / NB_TILE_K;
+    w->nb_tiles = img.n_pad / NB_TILE_N;
+    w->nb_splits = (w->nb_kb + NB_MAX_KBS - 1) / NB_MAX_KBS;
+    w->nb_kbs = (w->nb_kb + w->nb_splits - 1) / w->nb_splits;
+    w->nb_splits = (w->nb_kb + w->nb_kbs - 1) / w->nb_kbs;
+    const int last_ku = (w->nb_kb - (w->nb_splits - 1) * w->nb_kbs + NB_UK - 1) / NB_UK;
+    long long gj = sms / w->nb_splits;
+    if (gj < 1) gj = 1;
+    if (gj > (long long)w->nb_tiles * last_ku) gj = (long long)w->nb_tiles * last_ku;
+    w->nb_gj = (int)gj;
+    const size_t partial_bytes = (size_t)w->nb_splits * ((size_t)w->nb_tiles + w->nb_gj) * (NB_ROWS / 4) * NB_TILE_N * sizeof(float);
+    const size_t counter_bytes = (size_t)w->nb_tiles * 4 * sizeof(unsigned int);
+    // which blocks hold a part of which column tile: block c of a range owns units [tot * c / gj, tot * (c + 1) / gj)
+    std::vector<uint32_t> sched((size_t)(1 + w->nb_splits) * w->nb_tiles, 0u);
+    for (int jj = 0; jj < w->nb_splits; ++jj) {
+        const long long kbn = std::min(w->nb_kbs, w->nb_kb - jj * w->nb_kbs), kun = (kbn + NB_UK - 1) / NB_UK, tot = (long long)w->nb_tiles * kun;
+        for (int t = 0; t < w->nb_tiles; ++t) {
+            const long long fu = (long long)t * kun, lu = fu + kun - 1;
+            const long long cf = ((fu + 1) * gj + tot - 1) / tot - 1, cl = ((lu + 1) * gj + tot - 1) / tot - 1;
+            sched[(size_t)t] += (uint32_t)(cl - cf + 1);
+            sched[(size_t)(1 + jj) * w->nb_tiles + t] = (uint32_t)cf | ((uint32_t)cl << 16);
+        }
+    }
+    CU_TRY(cudaMalloc(&w->d_nb_sched, sched.size() * sizeof(uint32_t)));
+    CU_TRY(cudaMemcpy(w->d_nb_sched, sched.data(), sched.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+    CU_TRY(cudaMalloc(&w->d_nb_partial, partial_bytes));
+    CU_TRY(cudaMalloc(&w->d_nb_counters, counter_bytes));
+    CU_TRY(cudaMemset(w->d_nb_counters, 0, counter_bytes));
+    w->scratch_bytes += partial_bytes + counter_bytes;
+    CU_TRY(cudaDeviceSynchronize());
+    return TLLM_OK;
+}
+
+// `rows` activation rows through the decode tensor-core kernel, a launch per group of rows that fits its B operand
+int run_nb(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void* Y, int y_dtype, int y_ld, int epilogue, float scale, float scale2,
+           cudaStream_t st) {
+    const BsLayout& L = w->lay;
+    static std::mutex mu;
+    static bool configured[64] = {};
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (w->device < 64 && !configured[w->device]) {
+            CU_TRY(cudaFuncSetAttribute(nibble_spmm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            configured[w->device] = true;
+        }
+    }
+    NbParams p{};
+    p.partial = w->d_nb_partial;
+    p.counters = w->d_nb_counters;
+    p.sched = w->d_nb_sched;
+    p.status = w->d_status;
+    p.K = L.inners;
+    p.N = L.columns;
+    p.x_dtype = x_dtype;
+    p.x_ld = x_ld;
+    p.y_dtype = y_dtype;
+    p.y_ld = y_ld;
+    p.epilogue = epilogue;
+    p.P = x_dtype == TLLM_F32 ? 8 : 4;
+    p.KB = w->nb_kb;
+    p.KBS = w->nb_kbs;
+    p.k_splits = w->nb_splits;
+    p.n_tiles = w->nb_tiles;
+    p.Gj = w->nb_gj;
+    p.S = NB_MAX_STAGES;
+    // instruction descriptor: fp32 accumulate (bits 4-5 = 1), A = e2m1 (5, bits 7-9), B = e5m2 (1, bits 10-12), both
+    // K-major, N / 8 in bits 17-22, M / 16 in bits 24-28
+    p.idesc = (1u << 4) | (5u << 7) | (1u << 10) | ((uint32_t)(NB_ROWS >> 3) << 17) | ((uint32_t)(NB_TILE_N >> 4) << 24);
+    p.tmem_cols = 32;
+    p.tx_bytes = NB_A_TILE_BYTES;
+#ifdef NB_DEBUG
+    if (g_nb_debug_tx) p.tx_bytes = (uint32_t)g_nb_debug_tx;
+    if (g_nb_debug_stages) p.S = g_nb_debug_stages;
+    p.debug = g_nb_debug_flags;
+#endif
+    p.scale = scale;
+    p.scale2 = scale2;
+    const size_t smem = 1024 + (size_t)p.S * NB_UK * NB_A_STAGE_BYTES + (size_t)p.KBS * NB_ROWS * 128 + 512;
+    const size_t xe = dtype_size(x_dtype), ye = dtype_size(y_dtype);
+    const int per = nb_rows_per_launch(x_dtype);
+    for (int r0 = 0; r0 < rows; r0 += per) {
+        p.M = rows - r0 < per ? rows - r0 : per;
+        p.X = (const char*)X + (size_t)r0 * x_ld * xe;
+        p.Y = (char*)Y + (size_t)r0 * y_ld * ye;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)(p.k_splits * p.Gj));
+        cfg.blockDim = dim3(NB_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        CU_TRY(cudaLaunchKernelEx(&cfg, nibble_spmm_kernel, w->nib_map, p));
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        g_nb_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    return TLLM_OK;
+}
+
+enum KernelChoice { KERNEL_GATHER, KERNEL_MMA, KERNEL_NIBBLE };
+KernelChoice choose_kernel(const tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, int rows) {
+    const bool nb = nb_usable(w, x_dtype, x_layout, rows), mm = mm_usable(w, X, x_dtype, x_layout, x_ld, rows);
+    if (nb && mm) {
+        const int64_t entries = (int64_t)w->lay.inners * w->lay.columns;
+        const int forced = g_nb_max_rows.load(std::memory_order_relaxed);
+        if (forced > 0) return KERNEL_NIBBLE;
+        return mm_model_us(entries, rows) < nibble_model_us(entries, rows, nb_rows_per_launch(x_dtype)) ? KERNEL_MMA : KERNEL_NIBBLE;
+    }
+    return nb ? KERNEL_NIBBLE : (mm ? KERNEL_MMA : KERNEL_GATHER);
+}
+
 // K-tiles whose activation tables one launch keeps in shared memory at the same time (the rest follow, one barrier-
 // separated group after the other): small tables leave room for four blocks per SM
 #ifndef BS_RESIDENT_MAX
@@ -437,6 +607,7 @@ int create_from_dense(const int8_t* dense, int inners, int columns, float scale,
     tllm_weight* w = new tllm_weight();
     rc = upload(w, img, scale, max_rows);
     if (rc == TLLM_OK && !(opts && opts->no_bit_tiles)) rc = upload_bits(w, dense, inners, columns, sms);
+    if (rc == TLLM_OK && !(opts && opts->no_nibbles)) rc = upload_nibbles(w, dense, inners, columns, sms);
     if (rc != TLLM_OK) {
         tllm_weight_destroy(w);
         return rc;
@@ -505,6 +676,34 @@ int tllm_set_mma_min_rows(int rows) {
     g_mm_min_rows.store(rows < 0 ? -1 : rows, std::memory_order_relaxed);
     return prev;
 }
+
+int tllm_set_nibble_max_rows(int rows) {
+    return g_nb_max_rows.exchange(rows < 0 ? -1 : rows, std::memory_order_relaxed);
+}
+
+#ifdef NB_DEBUG
+int tllm_debug_set_nb_tx(int bytes) {
+    g_nb_debug_tx = bytes;
+    return 0;
+}
+int tllm_debug_set_nb_cg(int cg) {
+    g_nb_debug_cg = cg;
+    return 0;
+}
+int tllm_debug_set_nb_flags(int flags) {
+    g_nb_debug_flags = flags;
+    return 0;
+}
+int tllm_debug_set_nb_stages(int stages) {
+    g_nb_debug_stages = stages;
+    return 0;
+}
+int tllm_debug_set_nb_trace(void* device_buffer) {
+    CU_TRY(cudaMemcpyToSymbol(tllm::g_nb_trace, &device_buffer, sizeof(void*)));
+    return TLLM_OK;
+}
+#endif
+int64_t tllm_nibble_launch_count(void) { return g_nb_launches.load(std::memory_order_relaxed); }
 
 int tllm_ter_spmm(const void* X, int x_dtype, int x_layout, const int16_t* row_idx, const int32_t* col_off,
                   const int16_t* col_tile_idx, void* Y, int y_dtype, int batch, int rows, int columns,
@@ -581,6 +780,10 @@ int tllm_weight_destroy(tllm_weight* w) {
     cudaFree(w->d_bits);
     cudaFree(w->d_mm_partial);
     cudaFree(w->d_mm_counters);
+    cudaFree(w->d_nib);
+    cudaFree(w->d_nb_partial);
+    cudaFree(w->d_nb_counters);
+    cudaFree(w->d_nb_sched);
     cudaFree(w->d_partial);
     cudaFree(w->d_counters);
     cudaFree(w->d_status);
@@ -603,6 +806,7 @@ int tllm_weight_get_info(const tllm_weight* w, tllm_weight_info* info) {
     info->meta_bytes = (int64_t)w->meta_bytes;
     info->scratch_bytes = (int64_t)w->scratch_bytes;
     info->bit_tile_bytes = (int64_t)w->bits_bytes;
+    info->nibble_bytes = (int64_t)w->nib_bytes;
     info->scale = w->scale;
     return TLLM_OK;
 }
@@ -690,6 +894,11 @@ int tllm_weight_load(const char* path, tllm_weight** out) {
         w->mm_kb = h.mm_kb;
         rc = upload_bit_tiles(w, bits, sms);
     }
+    if (rc == TLLM_OK) {   // the four-bit planes are not stored: they are rebuilt from the lists
+        std::vector<int8_t> dense((size_t)h.inners * h.columns);
+        bs_unpack_dense(img, dense.data());
+        rc = upload_nibbles(w, dense.data(), h.inners, h.columns, sms);
+    }
     if (rc != TLLM_OK) {
         tllm_weight_destroy(w);
         return rc;
@@ -712,8 +921,9 @@ int tllm_weight_check(tllm_weight* w) {
         cudaMemset(w->d_status, 0, sizeof(int));
         cudaMemset(w->d_counters, 0, (size_t)w->lay.col_blocks * sizeof(unsigned int));
         if (w->d_mm_counters) cudaMemset(w->d_mm_counters, 0, (size_t)w->mm_n_tiles * 4 * sizeof(unsigned int));
+        if (w->d_nb_counters) cudaMemset(w->d_nb_counters, 0, (size_t)w->nb_tiles * 4 * sizeof(unsigned int));
         return fail(TLLM_ERR_KERNEL, "a bounded wait ran out inside the kernel (code %d: %s)", st,
-                    st == MM_ERR_WAIT ? "tensor-core pipeline stalled" : "block table never arrived");
+                    st == MM_ERR_WAIT ? "tensor-core pipeline stalled" : (st == NB_ERR_WAIT ? "decode tensor-core pipeline stalled" : "block table never arrived"));
     }
     return TLLM_OK;
 }
@@ -728,8 +938,9 @@ int tllm_spmm(tllm_weight* w, const void* X, int x_dtype, int x_layout, int rows
     if (rc) return rc;
     const BsLayout& L = w->lay;
     const int x_ld = x_layout == TLLM_ROW_MAJOR ? L.inners : rows;
-    if (mm_usable(w, X, x_dtype, x_layout, x_ld, rows))
-        return run_mm(w, X, x_dtype, x_ld, rows, Y, y_dtype, L.columns, 0, w->scale, 0.f, (cudaStream_t)stream);
+    const KernelChoice kc = choose_kernel(w, X, x_dtype, x_layout, x_ld, rows);
+    if (kc == KERNEL_NIBBLE) return run_nb(w, X, x_dtype, x_ld, rows, Y, y_dtype, L.columns, 0, w->scale, 0.f, (cudaStream_t)stream);
+    if (kc == KERNEL_MMA) return run_mm(w, X, x_dtype, x_ld, rows, Y, y_dtype, L.columns, 0, w->scale, 0.f, (cudaStream_t)stream);
     return run_gather(w, X, x_dtype, x_layout, x_ld, rows, Y, y_dtype, L.columns, 0, w->scale, 0.f, Scratch{w->d_partial, w->d_counters},
                       (cudaStream_t)stream);
 }
@@ -895,6 +1106,21 @@ int tllm_mlp_create(const int8_t* w_gate, const int8_t* w_up, const int8_t* w_do
     return TLLM_OK;
 }
 
+int tllm_mlp_create_cpu_format(int kind, int group, int chunk, int ri32, const int32_t* meta_gate, const void* ri_gate,
+                               const int32_t* meta_up, const void* ri_up, const int32_t* meta_down, const void* ri_down, int hidden,
+                               int intermediate, const tllm_pack_opts* opts, tllm_mlp** out) {
+    if (!meta_gate || !ri_gate || !meta_up || !ri_up || !meta_down || !ri_down || hidden <= 0 || intermediate <= 0 || !out)
+        return fail(TLLM_ERR_ARG, "tllm_mlp_create_cpu_format: bad argument");
+    if (kind < 1 || kind > 5) return fail(TLLM_ERR_ARG, "tllm_mlp_create_cpu_format: kind must be 1..5 (the single-array formats)");
+    *out = nullptr;
+    std::vector<int8_t> g, u, d;
+    const char* msg = tllm::decode_cpu_format(kind, group, chunk, meta_gate, ri_gate, ri32, 0, intermediate, hidden, &g);
+    if (!msg) msg = tllm::decode_cpu_format(kind, group, chunk, meta_up, ri_up, ri32, 0, intermediate, hidden, &u);
+    if (!msg) msg = tllm::decode_cpu_format(kind, group, chunk, meta_down, ri_down, ri32, 0, hidden, intermediate, &d);
+    if (msg) return fail(TLLM_ERR_ARG, "tllm_mlp_create_cpu_format: %s", msg);
+    return tllm_mlp_create(g.data(), u.data(), d.data(), hidden, intermediate, 1.f, 1.f, 1.f, opts, out);
+}
+
 int tllm_mlp_destroy(tllm_mlp* m) {
     if (!m) return TLLM_OK;
     tllm_weight_destroy(m->gate_up);
@@ -920,22 +1146,33 @@ int tllm_mlp_forward_ex(tllm_mlp* m, const void* X, int x_dtype, int rows, void*
     if (rc) return rc;
     char* h = (char*)(H ? H : m->d_h);
     cudaStream_t st = (cudaStream_t)stream;
-    if (mm_usable(m->gate_up, X, x_dtype, TLLM_ROW_MAJOR, m->hidden, rows) && mm_usable(m->down, h, x_dtype, TLLM_ROW_MAJOR, m->inter, rows)) {
-        rc = run_mm(m->gate_up, X, x_dtype, m->hidden, rows, h, x_dtype, m->inter, 1, m->s_gate, m->s_up, st);
-        if (rc) return rc;
-        return run_mm(m->down, h, x_dtype, m->inter, rows, Y, y_dtype, m->hidden, 0, m->down->scale, 0.f, st);
-    }
-    rc = run_gather(m->gate_up, X, x_dtype, TLLM_ROW_MAJOR, m->hidden, rows, h, x_dtype, m->inter, 1, m->s_gate, m->s_up,
-                    Scratch{m->gate_up->d_partial, m->gate_up->d_counters}, st);
+    // the two products pick their kernel independently (gate and up share the first one: its epilogue applies SiLU and the product)
+    const KernelChoice k1 = choose_kernel(m->gate_up, X, x_dtype, TLLM_ROW_MAJOR, m->hidden, rows);
+    if (k1 == KERNEL_NIBBLE) rc = run_nb(m->gate_up, X, x_dtype, m->hidden, rows, h, x_dtype, m->inter, 1, m->s_gate, m->s_up, st);
+    else if (k1 == KERNEL_MMA) rc = run_mm(m->gate_up, X, x_dtype, m->hidden, rows, h, x_dtype, m->inter, 1, m->s_gate, m->s_up, st);
+    else rc = run_gather(m->gate_up, X, x_dtype, TLLM_ROW_MAJOR, m->hidden, rows, h, x_dtype, m->inter, 1, m->s_gate, m->s_up,
+                         Scratch{m->gate_up->d_partial, m->gate_up->d_counters}, st);
     if (rc) return rc;
+    const KernelChoice k2 = choose_kernel(m->down, h, x_dtype, TLLM_ROW_MAJOR, m->inter, rows);
+    if (k2 == KERNEL_NIBBLE) return run_nb(m->down, h, x_dtype, m->inter, rows, Y, y_dtype, m->hidden, 0, m->down->scale, 0.f, st);
+    if (k2 == KERNEL_MMA) return run_mm(m->down, h, x_dtype, m->inter, rows, Y, y_dtype, m->hidden, 0, m->down->scale, 0.f, st);
     return run_gather(m->down, h, x_dtype, TLLM_ROW_MAJOR, m->inter, rows, Y, y_dtype, m->hidden, 0, m->down->scale, 0.f,
                       Scratch{m->down->d_partial, m->down->d_counters}, st);
 }
 
-int tllm_mlp_forward_host(tllm_mlp* m, void* X, int x_dtype, int rows, void* H) {
+// [a][b] -> [b][a] for elements of `e` bytes
+static void transpose_bytes(const void* src, void* dst, size_t a, size_t b, size_t e) {
+    const char* s = (const char*)src;
+    char* d = (char*)dst;
+    for (size_t i = 0; i < a; ++i)
+        for (size_t j = 0; j < b; ++j) memcpy(d + (j * a + i) * e, s + (i * b + j) * e, e);
+}
+
+int tllm_mlp_forward_host(tllm_mlp* m, void* X, int x_dtype, int x_layout, int rows, void* H) {
     if (!m || !X) return fail(TLLM_ERR_ARG, "tllm_mlp_forward_host: NULL pointer");
     if (rows <= 0) return fail(TLLM_ERR_ARG, "tllm_mlp_forward_host: rows must be positive");
     if (x_dtype != TLLM_F32 && x_dtype != TLLM_F16 && x_dtype != TLLM_BF16) return fail(TLLM_ERR_ARG, "tllm_mlp_forward_host: unsupported dtype");
+    if (x_layout != TLLM_ROW_MAJOR && x_layout != TLLM_COL_MAJOR) return fail(TLLM_ERR_ARG, "tllm_mlp_forward_host: unknown layout");
     tllm_weight* w = m->gate_up;
     int rc = check_device(w, "tllm_mlp_forward_host");
     if (rc) return rc;
@@ -948,13 +1185,27 @@ int tllm_mlp_forward_host(tllm_mlp* m, void* X, int x_dtype, int rows, void* H) 
     if (rc) return rc;
     rc = ensure(&m->d_h, &m->h_cap, hb, false);
     if (rc) return rc;
-    CU_TRY(cudaMemcpyAsync(m->d_x, X, xb, cudaMemcpyHostToDevice, w->own_stream));
+    // a column-major caller ([hidden][rows], rows contiguous) is turned on the host: the block itself is row-major
+    const bool turn = x_layout == TLLM_COL_MAJOR && rows > 1;
+    std::vector<char> tx, th;
+    void* hx = X;
+    if (turn) {
+        tx.resize(xb);
+        transpose_bytes(X, tx.data(), (size_t)m->hidden, (size_t)rows, e);
+        hx = tx.data();
+        if (H) th.resize(hb);
+    }
+    CU_TRY(cudaMemcpyAsync(m->d_x, hx, xb, cudaMemcpyHostToDevice, w->own_stream));
     rc = tllm_mlp_forward(m, m->d_x, x_dtype, rows, m->d_y, m->d_h, w->own_stream);
     if (rc) return rc;
-    CU_TRY(cudaMemcpyAsync(X, m->d_y, xb, cudaMemcpyDeviceToHost, w->own_stream));
-    if (H) CU_TRY(cudaMemcpyAsync(H, m->d_h, hb, cudaMemcpyDeviceToHost, w->own_stream));
+    CU_TRY(cudaMemcpyAsync(hx, m->d_y, xb, cudaMemcpyDeviceToHost, w->own_stream));
+    if (H) CU_TRY(cudaMemcpyAsync(turn ? (void*)th.data() : H, m->d_h, hb, cudaMemcpyDeviceToHost, w->own_stream));
     CU_TRY(cudaMemcpyAsync(w->h_status, w->d_status, sizeof(int), cudaMemcpyDeviceToHost, w->own_stream));
     CU_TRY(cudaStreamSynchronize(w->own_stream));
+    if (turn) {
+        transpose_bytes(tx.data(), X, (size_t)rows, (size_t)m->hidden, e);
+        if (H) transpose_bytes(th.data(), H, (size_t)rows, (size_t)m->inter, e);
+    }
     if (*w->h_status) return tllm_weight_check(w);
     return tllm_weight_check(m->down);
 }

@@ -5,16 +5,19 @@
 // convert_to_ter_tiled_mcsc, inter_tile_swizzle) and consumes what ternaryLLM_CPU/src/TCSC.hpp:6-409
 // (SparseFormat, MergedTCSC, MergedTCSC_Group) produce.
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <numeric>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../../include/tllm.h"
 #include "column_lists.h"
 #include "bstream_format.h"
+#include "nibble_format.h"
 #include "util.h"
 
 namespace {
@@ -443,10 +446,20 @@ extern "C" int tllm_pack_roundtrip(const int8_t* w, int inners, int columns, con
         if (std::memcmp(back.data(), w, back.size()) != 0) return tllm::fail(TLLM_ERR_ARG, "bit tiles do not reproduce the matrix");
         bit_bytes = (int64_t)bits.size() * 4;
     }
+    int64_t nibble_bytes = 0;
+    {   // and so must the third
+        NbHostImage nb;
+        nb_pack_dense(w, inners, columns, &nb);
+        std::vector<int8_t> back((size_t)inners * columns);
+        if (!nb_unpack_dense(nb, back.data()) || std::memcmp(back.data(), w, back.size()) != 0)
+            return tllm::fail(TLLM_ERR_ARG, "nibble planes do not reproduce the matrix");
+        nibble_bytes = (int64_t)nb.codes.size();
+    }
     if (info) {
         std::memset(info, 0, sizeof *info);
         tllm::bs_fill_info(img.lay, info);
         info->bit_tile_bytes = bit_bytes;
+        info->nibble_bytes = nibble_bytes;
         info->stream_bytes = (int64_t)img.stream.size();
         info->meta_bytes = (int64_t)img.meta.size() * 4;
     }
@@ -483,4 +496,55 @@ extern "C" int tllm_pack_corrupt_check(const int8_t* w, int inners, int columns,
     msg = bs_validate(img);
     if (msg) return tllm::fail(TLLM_ERR_ARG, "%s", msg);
     return TLLM_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// nibble planes: the transposed four-bit copy the decode tensor-core kernel reads (layout: nibble_format.h)
+// ---------------------------------------------------------------------------------------------------
+void nb_pack_dense(const int8_t* w, int inners, int columns, NbHostImage* out) {
+    out->inners = inners, out->columns = columns;
+    out->k_pad = (inners + 127) / 128 * 128, out->n_pad = (columns + 127) / 128 * 128;
+    const size_t pitch = (size_t)out->k_pad / 2;
+    out->codes.assign((size_t)out->n_pad * pitch, 0);
+    const int tiles = out->n_pad / 128;
+    std::atomic<int> next{0};
+    // one column tile at a time: its 128 rows of the image are private to the thread that builds it
+    auto work = [&]() {
+        for (;;) {
+            const int t = next.fetch_add(1);
+            if (t >= tiles) return;
+            const int n0 = t * 128, n1 = std::min(columns, n0 + 128);
+            uint8_t* base = out->codes.data() + (size_t)n0 * pitch;
+            for (int k = 0; k < inners; ++k) {
+                const int8_t* row = w + (size_t)k * columns;
+                const int shift = (k & 1) * 4;
+                uint8_t* dst = base + (k >> 1);
+                for (int n = n0; n < n1; ++n) {
+                    const int8_t v = row[n];
+                    if (v) dst[(size_t)(n - n0) * pitch] |= (uint8_t)((v > 0 ? NB_CODE_POS : NB_CODE_NEG) << shift);
+                }
+            }
+        }
+    };
+    unsigned nthreads = std::max(1u, std::min(std::thread::hardware_concurrency(), 32u));
+    nthreads = std::min<unsigned>(nthreads, (unsigned)tiles);
+    std::vector<std::thread> pool;
+    for (unsigned i = 1; i < nthreads; ++i) pool.emplace_back(work);
+    work();
+    for (std::thread& th : pool) th.join();
+}
+
+bool nb_unpack_dense(const NbHostImage& img, int8_t* w) {
+    const size_t pitch = (size_t)img.k_pad / 2;
+    for (int n = 0; n < img.n_pad; ++n)
+        for (int k = 0; k < img.k_pad; ++k) {
+            const uint32_t c = (img.codes[(size_t)n * pitch + (k >> 1)] >> ((k & 1) * 4)) & 0xFu;
+            if (c != 0 && c != NB_CODE_POS && c != NB_CODE_NEG) return false;
+            if (n >= img.columns || k >= img.inners) {
+                if (c) return false;
+                continue;
+            }
+            w[(size_t)k * img.columns + n] = c == 0 ? 0 : (c == NB_CODE_POS ? 1 : -1);
+        }
+    return true;
 }

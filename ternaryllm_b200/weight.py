@@ -9,8 +9,8 @@ from . import _lib
 from ._lib import PackOpts, WeightInfo, check, lib, np_ptr
 
 
-def _opts(tile_rows=0, num_ctas=0, max_rows=0, k_splits=0, no_bit_tiles=0):
-    return PackOpts(int(tile_rows), int(num_ctas), 0, int(max_rows), int(k_splits), int(no_bit_tiles))
+def _opts(tile_rows=0, num_ctas=0, max_rows=0, k_splits=0, no_bit_tiles=0, no_nibbles=0):
+    return PackOpts(int(tile_rows), int(num_ctas), 0, int(max_rows), int(k_splits), int(no_bit_tiles), int(no_nibbles))
 
 
 def _dense_i8(w):

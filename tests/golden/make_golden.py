@@ -80,9 +80,52 @@ def gen_python_packers(ref_root, out):
             tcsc_pos_idx=tpi.numpy().astype(np.int32), tcsc_pos_off=tpo.numpy().astype(np.int32),
             mcsc_idx=mi.numpy().astype(np.int32), mcsc_off=mo.numpy().astype(np.int32),
         )
+    gen_cpp_packers(cases)
     flat = {f"{c}.{k}": v for c, d in cases.items() for k, v in d.items()}
     np.savez_compressed(out, **flat)
     print("wrote", out, os.path.getsize(out), "bytes")
+
+
+def gen_cpp_packers(cases):
+    """Adds to every case what the reference's C++ packers return for its matrix (the host side of
+    ternaryLLM_GPU/csrc/ter_spmm_wrapper.cu: convert_to_ter_csc :9-72, convert_to_ter_tiled_csc :75-153,
+    convert_to_ter_tiled_mcsc :156-315 -- the one with the truncating step :277-291), without padding and with
+    padding to 4 and to 8.  Needs oracle/_ref/gpu_ext (python oracle/build_ref.py --gpu-ext); two further matrices
+    at a tile size the reference uses (256) are added so that the truncation and the tile order are exercised on
+    tiles with tens of entries."""
+    import glob
+
+    import torch
+
+    ext = glob.glob(os.path.join(ROOT, "oracle", "_ref", "gpu_ext", "ter_spmm*.so"))
+    assert ext, "run python oracle/build_ref.py --gpu-ext first"
+    spec = importlib.util.spec_from_file_location("ter_spmm", ext[0])
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    rng = np.random.default_rng(20250101)
+    for name, (K, N, T, s) in {"e": (512, 12, 256, 0.5), "f": (1024, 6, 256, 0.8)}.items():
+        w = random_ternary(rng, K, N, s)
+        if name == "f":
+            w[256:512, 2] = 0
+            w[:, 4] = -1
+        cases[name] = dict(w=w.astype(np.int8), T=np.int32(T))
+    for name, c in cases.items():
+        w = torch.tensor(c["w"].astype(np.int32)).contiguous()
+        K, N = w.shape
+        T = int(c["T"])
+        pos, neg = int((w == 1).sum()), int((w == -1).sum())
+        ni, no, pi, po = mod.convert_to_ter_csc(w, N, K, pos, neg)
+        c.update(cpp_csc_neg_idx=np.array(ni, np.int32), cpp_csc_neg_off=np.array(no, np.int32),
+                 cpp_csc_pos_idx=np.array(pi, np.int32), cpp_csc_pos_off=np.array(po, np.int32))
+        ni, no, pi, po = mod.convert_to_ter_tiled_csc(w, N, K, pos, neg, T)
+        c.update(cpp_tcsc_neg_idx=np.array(ni, np.int32), cpp_tcsc_neg_off=np.array(no, np.int32),
+                 cpp_tcsc_pos_idx=np.array(pi, np.int32), cpp_tcsc_pos_off=np.array(po, np.int32))
+        for tag, pad, padsz in (("nopad", False, 4), ("pad4", True, 4), ("pad8", True, 8)):
+            idx, off, til = mod.convert_to_ter_tiled_mcsc(w, N, K, pos, neg, T, pad, padsz)
+            c[f"cpp_mcsc_{tag}_idx"] = np.array(idx, np.int32)
+            c[f"cpp_mcsc_{tag}_off"] = np.array(off, np.int32)
+            c[f"cpp_mcsc_{tag}_til"] = np.array(til, np.int32)
+    print("reference C++ packers:", ext[0])
 
 
 def gen_cpu(out):
@@ -265,7 +308,11 @@ def gen_cpu(out):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("TLLM_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--ref", default=None, help="checkout of the reference project (default: $TLLM_REFERENCE_ROOT, else ../reference)")
     a = ap.parse_args()
+    if a.ref is None:
+        import oracle
+
+        a.ref = oracle.reference_root()
     gen_python_packers(a.ref, os.path.join(HERE, "gpu_packers.npz"))
     gen_cpu(os.path.join(HERE, "cpu_reference.npz"))
