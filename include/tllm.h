@@ -109,6 +109,16 @@ int tllm_convert_to_ter_tiled_mcsc(const int32_t* w, int columns, int inners, in
 int tllm_ter_spmm(const void* X, int x_dtype, int x_layout, const int16_t* row_idx, const int32_t* col_off,
                   const int16_t* col_tile_idx, void* Y, int y_dtype, int batch, int rows, int columns,
                   int inners, int tile_k, float scale, int uniformed, int padded, void* stream);
+/* Repacks one weight held in the reference's device arrays (row_idx int16, col_off int32, as
+ * ternaryLLM_GPU/TernaryLLM/TernaryLinear.py:144-146 registers them) into this library's formats, once, and remembers
+ * it under the arrays' addresses, the shape and the current device.  Every later tllm_ter_spmm call with the same
+ * arrays runs the packed kernels (gather, or a tensor-core kernel where the cost model prefers it) instead of the
+ * one-warp-per-column kernel on the arrays as they are -- so code written against the reference's three buffers gets
+ * the fast path without holding a handle.  Copies the arrays to the host, allocates and synchronises: call it at
+ * set-up time, not inside a stream capture.  The arrays must not change or be freed while remembered;
+ * tllm_ter_spmm_forget(row_idx, col_off) drops one weight (both NULL: all) and returns how many it dropped. */
+int tllm_ter_spmm_prepare(const int16_t* row_idx, const int32_t* col_off, int columns, int inners, int tile_k);
+int tllm_ter_spmm_forget(const int16_t* row_idx, const int32_t* col_off);
 
 /* --------------------------------------------------------------------------------------------------
  * Packed weights in the library's own B200 stream format (the replacement for

@@ -47,6 +47,8 @@ SIGNATURES = {
     "tllm_ter_tiled_mcsc_len": (_L, [_P, _I, _I, _I, _I, _I, _I]),
     "tllm_convert_to_ter_tiled_mcsc": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _L, _P, _P]),
     "tllm_ter_spmm": (_I, [_P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P]),
+    "tllm_ter_spmm_prepare": (_I, [_P, _P, _I, _I, _I]),
+    "tllm_ter_spmm_forget": (_I, [_P, _P]),
     "tllm_ternarize": (_I, [_P, _I, _I, _F, _F, _P, _P]),
     "tllm_weight_save": (_I, [_P, C.c_char_p]),
     "tllm_weight_load": (_I, [C.c_char_p, _P]),

@@ -677,6 +677,60 @@ int tllm_set_mma_min_rows(int rows) {
     return prev;
 }
 
+// ---- packed copies of the reference's device arrays, keyed by the arrays' addresses and the shape --------------------
+namespace {
+struct TerCacheEntry {
+    const void* row_idx;
+    const void* col_off;
+    int columns, inners, tile_k, device;
+    tllm_weight* w;
+};
+std::mutex g_ter_mu;
+std::vector<TerCacheEntry> g_ter_cache;
+
+tllm_weight* ter_cache_find(const void* row_idx, const void* col_off, int columns, int inners, int tile_k) {
+    std::lock_guard<std::mutex> lk(g_ter_mu);
+    if (g_ter_cache.empty()) return nullptr;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    for (const TerCacheEntry& e : g_ter_cache)
+        if (e.row_idx == row_idx && e.col_off == col_off && e.columns == columns && e.inners == inners && e.tile_k == tile_k && e.device == dev) return e.w;
+    return nullptr;
+}
+}  // namespace
+
+int tllm_ter_spmm_prepare(const int16_t* row_idx, const int32_t* col_off, int columns, int inners, int tile_k) {
+    if (!row_idx || !col_off || columns <= 0 || inners <= 0 || tile_k <= 0) return fail(TLLM_ERR_ARG, "tllm_ter_spmm_prepare: bad argument");
+    if (ter_cache_find(row_idx, col_off, columns, inners, tile_k)) return TLLM_OK;
+    // the row-index array's length is the largest list end
+    const size_t n_off = (size_t)columns * ((size_t)(inners + tile_k - 1) / tile_k) * 4;
+    std::vector<int32_t> off(n_off);
+    CU_TRY(cudaMemcpy(off.data(), col_off, n_off * sizeof(int32_t), cudaMemcpyDeviceToHost));
+    int64_t len = 0;
+    for (size_t i = 0; i < n_off; i += 4) len = std::max<int64_t>(len, off[i + 2]);
+    tllm_weight* w = nullptr;
+    const int rc = tllm_weight_create_mcsc_device(row_idx, len, col_off, columns, inners, tile_k, 1.0f, nullptr, &w);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lk(g_ter_mu);
+    g_ter_cache.push_back(TerCacheEntry{row_idx, col_off, columns, inners, tile_k, w->device, w});
+    return TLLM_OK;
+}
+
+int tllm_ter_spmm_forget(const int16_t* row_idx, const int32_t* col_off) {
+    std::vector<tllm_weight*> dead;
+    {
+        std::lock_guard<std::mutex> lk(g_ter_mu);
+        for (size_t i = 0; i < g_ter_cache.size();) {
+            if ((!row_idx && !col_off) || (g_ter_cache[i].row_idx == row_idx && g_ter_cache[i].col_off == col_off)) {
+                dead.push_back(g_ter_cache[i].w);
+                g_ter_cache.erase(g_ter_cache.begin() + (long)i);
+            } else ++i;
+        }
+    }
+    for (tllm_weight* w : dead) tllm_weight_destroy(w);
+    return (int)dead.size();
+}
+
 int tllm_set_nibble_max_rows(int rows) {
     return g_nb_max_rows.exchange(rows < 0 ? -1 : rows, std::memory_order_relaxed);
 }
@@ -717,6 +771,27 @@ int tllm_ter_spmm(const void* X, int x_dtype, int x_layout, const int16_t* row_i
     const int rc = check_types(x_dtype, y_dtype, "tllm_ter_spmm");
     if (rc) return rc;
     if (batch > 65535) return fail(TLLM_ERR_ARG, "tllm_ter_spmm: batch too large");
+    if (tllm_weight* w = ter_cache_find(row_idx, col_off, columns, inners, tile_k)) {
+        // these arrays were repacked by tllm_ter_spmm_prepare: the product runs on the packed copy
+        const BsLayout& L = w->lay;
+        cudaStream_t st = (cudaStream_t)stream;
+        const size_t xe = dtype_size(x_dtype), ye = dtype_size(y_dtype);
+        if (x_layout == TLLM_ROW_MAJOR) {
+            const long long m = (long long)batch * rows;      // the batch is contiguous: one product of batch * rows rows
+            if (m > 0x7fffffffLL) return fail(TLLM_ERR_ARG, "tllm_ter_spmm: batch * rows too large");
+            const KernelChoice kc = choose_kernel(w, X, x_dtype, x_layout, inners, (int)m);
+            if (kc == KERNEL_NIBBLE) return run_nb(w, X, x_dtype, inners, (int)m, Y, y_dtype, columns, 0, scale, 0.f, st);
+            if (kc == KERNEL_MMA) return run_mm(w, X, x_dtype, inners, (int)m, Y, y_dtype, columns, 0, scale, 0.f, st);
+            return run_gather(w, X, x_dtype, x_layout, inners, (int)m, Y, y_dtype, columns, 0, scale, 0.f, Scratch{w->d_partial, w->d_counters}, st);
+        }
+        for (int b = 0; b < batch; ++b) {
+            const int rc2 = run_gather(w, (const char*)X + (size_t)b * rows * inners * xe, x_dtype, x_layout, rows, rows,
+                                       (char*)Y + (size_t)b * rows * columns * ye, y_dtype, columns, 0, scale, 0.f, Scratch{w->d_partial, w->d_counters}, st);
+            if (rc2) return rc2;
+        }
+        (void)L;
+        return TLLM_OK;
+    }
     constexpr int MC = 4;
     dim3 grid((columns + 7) / 8, (rows + MC - 1) / MC, batch), block(256);
     if (grid.y > 65535) return fail(TLLM_ERR_ARG, "tllm_ter_spmm: too many rows for one call");

@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(NB_THREADS, 1) nibble_spmm_kernel(const __grid
         NB_ACC_DECL;
         for (int u = u0; u < u1; ++u) {
             NB_CLK(c0);
-            NB_WAIT(A_EMPTY(s), sph ^ 1u);
+            NB_WAIT_BLOCK(A_EMPTY(s), sph ^ 1u);      // parked, not spinning: this wait is long while B is not ready
             NB_CLK(c1);
             NB_ACC(8, c1 - c0);
             if (elect_one()) {
@@ -441,7 +441,7 @@ __global__ void __launch_bounds__(NB_THREADS, 1) nibble_spmm_kernel(const __grid
         const uint32_t a_lo0 = (a_base >> 4) & 0x3FFFu, b_lo0 = (b_base >> 4) & 0x3FFFu;
         uint32_t s = 0, sph = 0, a = 0, aph = 0;
         NB_ACC_DECL;
-        NB_WAIT(B_READY, 0u);
+        NB_WAIT_BLOCK(B_READY, 0u);                   // parked: B waits for the preceding kernel, whose blocks may share this SM
         tc_fence_after();
         int ku0 = u0 % KUj;
         for (int u = u0; u < u1;) {

@@ -90,6 +90,9 @@ def convert_to_ter_tiled_mcsc(w, columns, inners, cnt_pos, cnt_neg, TILE_K, padd
     return _ret((idx, off, til), as_numpy)
 
 
+AUTO_PREPARE = False
+
+
 def ter_spmm(X, w_tiled_merged_row_indice, w_tiled_merged_col_offset, w_col_tile_indices, batch_size, rows, columns,
              inners, uniformed, padded, scale=1.0, out=None, tile_k=None):
     """Product on the reference's merged tiled CSC arrays; returns [batch_size, rows, columns].
@@ -128,6 +131,8 @@ def ter_spmm(X, w_tiled_merged_row_indice, w_tiled_merged_col_offset, w_col_tile
     if batch_size == 0:
         return out                      # the reference launches nothing for an empty batch (TernaryLinear.py:168)
     tile_ptr = w_col_tile_indices.data_ptr() if w_col_tile_indices is not None and w_col_tile_indices.numel() else None
+    if AUTO_PREPARE and not torch.cuda.is_current_stream_capturing():
+        prepare(w_tiled_merged_row_indice, w_tiled_merged_col_offset, columns, inners, tile_k)
     with torch.cuda.device(X.device):
         check(lib().tllm_ter_spmm(X.data_ptr(), _lib.torch_dtype_code(X.dtype), layout, w_tiled_merged_row_indice.data_ptr(),
                                   w_tiled_merged_col_offset.data_ptr(), tile_ptr, out.data_ptr(), _lib.torch_dtype_code(y_dtype),
@@ -136,7 +141,30 @@ def ter_spmm(X, w_tiled_merged_row_indice, w_tiled_merged_col_offset, w_col_tile
     return out
 
 
-def install():
+def prepare(w_tiled_merged_row_indice, w_tiled_merged_col_offset, columns, inners, tile_k=None):
+    """Repack one weight held in the reference's device arrays, once (tllm_ter_spmm_prepare): later `ter_spmm` calls with
+    the same two tensors run the packed kernels.  The tensors must stay alive and unchanged; `forget` drops the copy."""
+    import torch
+
+    if tile_k is None:
+        tile_k = tile_size_for(inners)
+    with torch.cuda.device(w_tiled_merged_row_indice.device):
+        check(lib().tllm_ter_spmm_prepare(w_tiled_merged_row_indice.data_ptr(), w_tiled_merged_col_offset.data_ptr(), int(columns), int(inners),
+                                          int(tile_k)), "ter_spmm.prepare")
+
+
+def forget(w_tiled_merged_row_indice=None, w_tiled_merged_col_offset=None):
+    """Drops the packed copy made by `prepare` for these tensors (no arguments: all of them); returns how many."""
+    a = w_tiled_merged_row_indice.data_ptr() if w_tiled_merged_row_indice is not None else None
+    b = w_tiled_merged_col_offset.data_ptr() if w_tiled_merged_col_offset is not None else None
+    return int(lib().tllm_ter_spmm_forget(a, b))
+
+
+def install(auto_prepare=False):
+    """Make `import ter_spmm` resolve to this module (for unmodified reference code).  With auto_prepare, the first
+    `ter_spmm` call that sees a pair of weight tensors outside a stream capture repacks it (see `prepare`)."""
+    global AUTO_PREPARE
+    AUTO_PREPARE = bool(auto_prepare)
     """Make `import ter_spmm` resolve to this module (for unmodified reference code)."""
     sys.modules.setdefault("ter_spmm", sys.modules[__name__])
     return sys.modules["ter_spmm"]

@@ -77,6 +77,47 @@ def test_ter_spmm_on_golden_arrays(gpu_packers, case, dtype):
     assert np.array_equal(out[0].double().cpu().numpy(), oracle.dense_f64(xs[0], c["w"], 0.5))
 
 
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_ter_spmm_after_prepare_runs_the_packed_kernels(gpu_packers, dtype):
+    """tllm_ter_spmm_prepare repacks the reference's device arrays once; the same ter_spmm call then gives the same
+    values from the packed kernels (launch counters show which ran), for both activation layouts, and `forget` puts the
+    call back on the arrays as they are."""
+    L = _lib.lib()
+    rng = np.random.default_rng(21)
+    for case in ("a", "b", "c", "d", "e", "f"):
+        c = gpu_packers[case]
+        K, N = c["w"].shape
+        T = int(c["T"])
+        idx, off = (c["mcsc_idx"], c["mcsc_off"]) if "mcsc_idx" in c else oracle.ter_tiled_mcsc(c["w"].astype(np.int32), T)[:2]
+        ri = torch.tensor(np.asarray(idx).astype(np.int16), device=dev())
+        co = torch.tensor(np.asarray(off).astype(np.int32), device=dev())
+        til = torch.zeros(1, dtype=torch.int16, device=dev())
+        B, M = 2, 3
+        xs = rng.integers(-8, 9, size=(B, M, K)).astype(np.float64)
+        X = torch.tensor(xs, dtype=DT[dtype], device=dev())
+        before = ter_spmm.ter_spmm(X, ri, co, til, B, M, N, K, False, False, scale=0.25, tile_k=T)
+        ter_spmm.prepare(ri, co, N, K, tile_k=T)
+        ter_spmm.prepare(ri, co, N, K, tile_k=T)                  # a second call finds the copy
+        prev = L.tllm_set_nibble_max_rows(0), L.tllm_set_mma_min_rows(0)
+        n0 = L.tllm_launch_count()
+        after = ter_spmm.ter_spmm(X, ri, co, til, B, M, N, K, False, False, scale=0.25, tile_k=T)
+        assert L.tllm_launch_count() - n0 == 2                    # six rows: two gather launches of up to four rows, not one per-column launch
+        L.tllm_set_nibble_max_rows(64)
+        d0 = L.tllm_nibble_launch_count()
+        tensor = ter_spmm.ter_spmm(X, ri, co, til, B, M, N, K, False, False, scale=0.25, tile_k=T)
+        assert L.tllm_nibble_launch_count() > d0
+        L.tllm_set_nibble_max_rows(prev[0]), L.tllm_set_mma_min_rows(prev[1])
+        Xt = X.transpose(1, 2).contiguous()
+        turned = ter_spmm.ter_spmm(Xt, ri, co, til, B, M, N, K, False, False, scale=0.25, tile_k=T) if M != K else after
+        want = np.stack([oracle.dense_f64(xs[b], c["w"], 0.25) for b in range(B)])
+        for y in (before, after, tensor, turned):
+            assert np.array_equal(y.double().cpu().numpy(), want), case
+        assert ter_spmm.forget(ri, co) == 1 and ter_spmm.forget(ri, co) == 0
+        n0 = L.tllm_launch_count()
+        ter_spmm.ter_spmm(X, ri, co, til, B, M, N, K, False, False, scale=0.25, tile_k=T)
+        assert L.tllm_launch_count() - n0 == 1
+
+
 def test_ter_spmm_error_behaviour(gpu_packers):
     c = gpu_packers["a"]
     K, N = c["w"].shape

@@ -78,6 +78,36 @@ def test_mcsc_modes_against_oracle(K, N, T, s, pad):
         assert len(cidx) == len(oidx) and np.array_equal(cidx[:n], oidx[:n])
 
 
+@pytest.mark.parametrize("case", ["a", "b", "c", "d", "e", "f"])
+def test_packers_against_the_reference_cpp_packers(gpu_packers, case):
+    """The arrays the reference's own C++ packers returned for the fixture matrices (the host side of
+    ternaryLLM_GPU/csrc/ter_spmm_wrapper.cu, compiled where it lies and called by tests/golden/make_golden.py):
+    convert_to_ter_csc and convert_to_ter_tiled_csc entry for entry, and convert_to_ter_tiled_mcsc in its truncating
+    form (mode 1) entry for entry -- offsets, tile order, and every row id a list still refers to -- without padding
+    and with padding to 4 and to 8.  The C restatement in oracle/ is held to the same arrays."""
+    c = gpu_packers[case]
+    w = c["w"].astype(np.int32)
+    K, N = w.shape
+    T = int(c["T"])
+    pos, neg = int((w == 1).sum()), int((w == -1).sum())
+    ni, no, pi, po = ter_spmm.convert_to_ter_csc(w, N, K, pos, neg, as_numpy=True)
+    for got, key in ((ni, "cpp_csc_neg_idx"), (no, "cpp_csc_neg_off"), (pi, "cpp_csc_pos_idx"), (po, "cpp_csc_pos_off")):
+        assert np.array_equal(got, c[key]), key
+    ni, no, pi, po = ter_spmm.convert_to_ter_tiled_csc(w, N, K, pos, neg, T, as_numpy=True)
+    for got, key in ((ni, "cpp_tcsc_neg_idx"), (no, "cpp_tcsc_neg_off"), (pi, "cpp_tcsc_pos_idx"), (po, "cpp_tcsc_pos_off")):
+        assert np.array_equal(got, c[key]), key
+    for tag, pad, padsz in (("nopad", False, 4), ("pad4", True, 4), ("pad8", True, 8)):
+        want_idx, want_off, want_til = c[f"cpp_mcsc_{tag}_idx"], c[f"cpp_mcsc_{tag}_off"], c[f"cpp_mcsc_{tag}_til"]
+        for name, (idx, off, til) in (("library", ter_spmm.convert_to_ter_tiled_mcsc(w, N, K, pos, neg, T, pad, padsz, compat=True, as_numpy=True)),
+                                      ("oracle", oracle.ter_tiled_mcsc(w, T, padding=pad, padding_size=padsz, lossy=True))):
+            assert np.array_equal(off, want_off), (name, tag)
+            assert np.array_equal(til, want_til), (name, tag)
+            # every entry a list refers to; what lies between the truncated lists is whatever the next tile wrote
+            o = want_off.reshape(-1, 4)
+            for s0, s1 in zip(o[:, 0], o[:, 2]):
+                assert np.array_equal(idx[s0:s1], want_idx[s0:s1]), (name, tag)
+
+
 def _roundtrip(w, **opts):
     w = np.ascontiguousarray(w, np.int8)
     K, N = w.shape
