@@ -78,6 +78,21 @@ __global__ void __launch_bounds__(1024) push_allreduce_add_rmsnorm_kernel(const 
         __threadfence_system();
         st_release_sys(p.flags[tid] + (set * p.world + p.rank) * p.max_rows + r, e);
     }
+    // ---- what does not depend on the peers is read while their rows are on the way: the residual row and the norm weight
+    T* x = (T*)p.x + (size_t)r * p.hidden;
+    T* h = (T*)p.h + (size_t)r * p.hidden;
+    const T* wgt = (const T*)p.weight;
+    constexpr int KEEP = 2;             // vectors of the row a thread keeps in registers
+    const int nvec = p.hidden / NV;
+    float keep[KEEP][8], gain[KEEP][8];
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+        const int vi = tid + k * nt;
+        if (vi < nvec) {
+            RmsVec<T>::load(x + (size_t)vi * NV, keep[k]);
+            if (wgt) RmsVec<T>::load(wgt + (size_t)vi * NV, gain[k]);
+        }
+    }
     // ---- wait for every peer's row ----
     if (tid < p.world && tid != p.rank) {
         const uint32_t* f = p.flags[p.rank] + (set * p.world + tid) * p.max_rows + r;
@@ -93,17 +108,10 @@ __global__ void __launch_bounds__(1024) push_allreduce_add_rmsnorm_kernel(const 
     }
     __syncthreads();
     // ---- x += sum over ranks (rank order), h = x * rsqrt(mean(x^2) + eps) * weight ----
-    T* x = (T*)p.x + (size_t)r * p.hidden;
-    T* h = (T*)p.h + (size_t)r * p.hidden;
-    const T* wgt = (const T*)p.weight;
     const float* mine_recv = p.recv[p.rank] + (set * p.world * p.max_rows + r) * (size_t)p.hidden;   // slot of rank 0, row r
     const size_t slot_stride = (size_t)p.max_rows * p.hidden;
-    constexpr int KEEP = 2;             // vectors of the row a thread keeps between the two passes
-    float keep[KEEP][8];
     float ss = 0.f;
-    const int nvec = p.hidden / NV;
-    auto first_pass = [&](int vi, float (&v)[8]) {
-        RmsVec<T>::load(x + (size_t)vi * NV, v);
+    auto first_pass = [&](int vi, float (&v)[8]) {      // v holds the residual values on entry
         float s[8];
 #pragma unroll
         for (int i = 0; i < NV; ++i) s[i] = 0.f;
@@ -128,6 +136,7 @@ __global__ void __launch_bounds__(1024) push_allreduce_add_rmsnorm_kernel(const 
     }
     for (int vi = tid + KEEP * nt; vi < nvec; vi += nt) {
         float v[8];
+        RmsVec<T>::load(x + (size_t)vi * NV, v);
         first_pass(vi, v);
     }
 #pragma unroll
@@ -137,10 +146,8 @@ __global__ void __launch_bounds__(1024) push_allreduce_add_rmsnorm_kernel(const 
     float tot = 0.f;
     for (int w = 0; w < (nt + 31) / 32; ++w) tot += red[w];
     const float inv = rsqrtf(tot / (float)p.hidden + p.eps);
-    auto second_pass = [&](int vi, float (&v)[8]) {
-        if (wgt) {
-            float g[8];
-            RmsVec<T>::load(wgt + (size_t)vi * NV, g);
+    auto second_pass = [&](int vi, float (&v)[8], const float* g) {
+        if (g) {
 #pragma unroll
             for (int i = 0; i < NV; ++i) v[i] = v[i] * inv * g[i];
         } else {
@@ -152,12 +159,13 @@ __global__ void __launch_bounds__(1024) push_allreduce_add_rmsnorm_kernel(const 
 #pragma unroll
     for (int k = 0; k < KEEP; ++k) {
         const int vi = tid + k * nt;
-        if (vi < nvec) second_pass(vi, keep[k]);
+        if (vi < nvec) second_pass(vi, keep[k], wgt ? gain[k] : nullptr);
     }
     for (int vi = tid + KEEP * nt; vi < nvec; vi += nt) {
-        float v[8];
+        float v[8], g[8];
         RmsVec<T>::load(x + (size_t)vi * NV, v);
-        second_pass(vi, v);
+        if (wgt) RmsVec<T>::load(wgt + (size_t)vi * NV, g);
+        second_pass(vi, v, wgt ? g : nullptr);
     }
     if (tid == 0) p.epoch[r] = e;
 }

@@ -42,8 +42,7 @@ namespace tllm {
 #define NB_A_STAGE_BYTES 16384        // shared-memory footprint of a tile: 8 bytes of codes, 8 bytes of gap, ...
 #define NB_A_TILE_BYTES 8192          // bytes of a tile in global memory = bytes the copy reports to the barrier
 #define NB_ROWS 16                    // piece rows of B (the MMA's N)
-#define NB_UK 2                       // tiles per unit: one barrier round and one tcgen05.commit per unit
-#define NB_MAX_STAGES 4               // ring stages of one unit each
+#define NB_MAX_STAGES 4               // ring stages of one unit each (a unit is UK tiles: one barrier round and one tcgen05.commit)
 #define NB_MAX_KBS 32                 // K blocks of one range: B = 32 * 16 * 128 bytes = 64 KiB
 #define NB_THREADS 192
 #define NB_ERR_WAIT 4                 // status word: a bounded wait of this kernel ran out
@@ -342,7 +341,8 @@ __device__ __forceinline__ void nb_build_b(const NbParams& p, int ct, int lane, 
         }                      \
     } while (0)
 
-__global__ void __launch_bounds__(NB_THREADS, 1) nibble_spmm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ NbParams p) {
+template <int UK>
+__global__ void __launch_bounds__(NB_THREADS, UK == 1 ? 2 : 1) nibble_spmm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ NbParams p) {
     extern __shared__ unsigned char nb_smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(NB_THREADS, 1) nibble_spmm_kernel(const __grid
     const int j = blockIdx.x / p.Gj, cc = blockIdx.x % p.Gj, G = p.Gj;
     const int kbj0 = j * p.KBS;
     const int KBj = min(p.KBS, p.KB - kbj0);
-    const int KUj = (KBj + NB_UK - 1) / NB_UK;                    // units per column tile in this range
+    const int KUj = (KBj + UK - 1) / UK;                    // units per column tile in this range
     const long long total = (long long)p.n_tiles * KUj;
     const int u0 = (int)(total * cc / G), u1 = (int)(total * (cc + 1) / G);
     if (u0 >= u1) return;
@@ -360,7 +360,7 @@ __global__ void __launch_bounds__(NB_THREADS, 1) nibble_spmm_kernel(const __grid
     const uint32_t raw0 = smem_u32(nb_smem);
     const uint32_t base = (raw0 + 1023u) & ~1023u;                 // swizzled tiles need 1024-byte alignment
     const uint32_t S = (uint32_t)p.S;
-    const uint32_t a_stage = NB_UK * NB_A_STAGE_BYTES;
+    const uint32_t a_stage = UK * NB_A_STAGE_BYTES;
     const uint32_t a_base = base, b_base = a_base + S * a_stage;
     const uint32_t b_tile = NB_ROWS * 128u;                        // bytes of B per K block
     const uint32_t bar_base = b_base + (uint32_t)p.KBS * b_tile;
@@ -412,7 +412,7 @@ __global__ void __launch_bounds__(NB_THREADS, 1) nibble_spmm_kernel(const __grid
             NB_CLK(c1);
             NB_ACC(8, c1 - c0);
             if (elect_one()) {
-                const int nk = min(NB_UK, KBj - ku * NB_UK);
+                const int nk = min(UK, KBj - ku * UK);
 #ifdef NB_DEBUG
                 if (p.debug & 2) mbar_arrive(A_FULL(s));
                 else
@@ -420,9 +420,9 @@ __global__ void __launch_bounds__(NB_THREADS, 1) nibble_spmm_kernel(const __grid
                 {
                     mbar_expect_tx(A_FULL(s), (uint32_t)nk * p.tx_bytes);
 #pragma unroll
-                    for (int t = 0; t < NB_UK; ++t)
+                    for (int t = 0; t < UK; ++t)
                         if (t < nk)
-                            tma_load_2d(a_base + s * a_stage + (uint32_t)t * NB_A_STAGE_BYTES, &wmap, (kbj0 + ku * NB_UK + t) * NB_TILE_K, tile * NB_TILE_N,
+                            tma_load_2d(a_base + s * a_stage + (uint32_t)t * NB_A_STAGE_BYTES, &wmap, (kbj0 + ku * UK + t) * NB_TILE_K, tile * NB_TILE_N,
                                         A_FULL(s));
                 }
             }
@@ -461,15 +461,15 @@ __global__ void __launch_bounds__(NB_THREADS, 1) nibble_spmm_kernel(const __grid
 #ifdef NB_DEBUG
                 if (lane == 0 && u == u0 && ku == ku0) NB_STAMP(4);
 #endif
-                const int nk = min(NB_UK, KBj - ku * NB_UK);
-                const uint32_t a_lo = a_lo0 + s * (a_stage >> 4), b_lo = b_lo0 + (uint32_t)(ku * NB_UK) * (b_tile >> 4);
+                const int nk = min(UK, KBj - ku * UK);
+                const uint32_t a_lo = a_lo0 + s * (a_stage >> 4), b_lo = b_lo0 + (uint32_t)(ku * UK) * (b_tile >> 4);
                 if (elect_one()) {
 #ifdef NB_DEBUG
                     if (!(p.debug & 1))
 #endif
                     {
 #pragma unroll
-                        for (uint32_t t = 0; t < NB_UK; ++t)
+                        for (uint32_t t = 0; t < UK; ++t)
                             if ((int)t < nk) {
 #pragma unroll
                                 for (uint32_t k4 = 0; k4 < NB_TILE_K / 32; ++k4)       // 32 values = 32 bytes = 2 descriptor address units

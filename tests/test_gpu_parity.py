@@ -102,7 +102,7 @@ def test_ter_spmm_after_prepare_runs_the_packed_kernels(gpu_packers, dtype):
         n0 = L.tllm_launch_count()
         after = ter_spmm.ter_spmm(X, ri, co, til, B, M, N, K, False, False, scale=0.25, tile_k=T)
         assert L.tllm_launch_count() - n0 == 2                    # six rows: two gather launches of up to four rows, not one per-column launch
-        L.tllm_set_nibble_max_rows(64)
+        L.tllm_set_mma_min_rows(-1), L.tllm_set_nibble_max_rows(64)
         d0 = L.tllm_nibble_launch_count()
         tensor = ter_spmm.ter_spmm(X, ri, co, til, B, M, N, K, False, False, scale=0.25, tile_k=T)
         assert L.tllm_nibble_launch_count() > d0

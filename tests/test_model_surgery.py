@@ -102,4 +102,4 @@ def test_prepared_model_runs_the_mlp_on_the_packed_kernel():
     y = mlp(x.cuda())
     assert _lib.lib().tllm_launch_count() >= before + 3
     want = rmlp.double()(x.double())
-    assert float((y.double().cpu() - want).abs().max()) <= 1e-4 * float(want.abs().max())
+    assert float((y.detach().double().cpu() - want.detach()).abs().max()) <= 1e-4 * float(want.detach().abs().max())
