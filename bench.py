@@ -431,6 +431,11 @@ def decoder_bench(torch, dist, world, rank, device, steps, warmup, sparsities, b
             if headline is None:
                 headline, clocks = rec, clk.summary()
                 rec["breakdown_us_per_layer"] = layer_breakdown(torch, layers[0], x0, reduce)
+                us_launch, per_layer = products_only(torch, layers[:nsets], x0)
+                balg_launch = layers[0].alg_bytes_local / per_layer
+                rec["products_only"] = {"us_per_launch": us_launch, "launches_per_layer": per_layer, "algorithmic_bytes_per_launch": balg_launch,
+                                        "algorithmic_GBps": balg_launch / us_launch / 1e3,
+                                        "kernel": "nibble_spmm_kernel" if decode_tc_launches else ("mma_spmm_kernel" if tensor_launches else "bstream_spmm_kernel")}
             records.append(rec)
             note(f"{S:.0%} zeros, batch {batch}: {rec['tokens_per_s']:.1f} tokens/s ({ms:.2f} ms/step)")
             del graph
@@ -470,6 +475,32 @@ def layer_breakdown(torch, layer, x0, reduce, reps=20):
     torch.cuda.synchronize()
     names = ["reduce+add+norm (MLP)", "QKV product", "attention core and cache write (stock)", "O product", "reduce+add+norm (attention)", "MLP products"]
     return {n: float(np.median([ev[r][i].elapsed_time(ev[r][i + 1]) for r in range(3, reps)])) * 1e3 for i, n in enumerate(names)}
+
+
+def products_only(torch, layers, x0, reps=10):
+    """The four ternary products of a layer (QKV, O, gate|up + down) back to back over the distinct weight sets, from one
+    CUDA graph, no glue in between: (mean microseconds per launch, launches per layer).  The dominant kernel of the
+    decoder step timed on its own, live."""
+    M = x0.shape[0]
+    h = x0.clone()
+    a = torch.randn((M, layers[0].hq * layers[0].hd), device=x0.device).to(x0.dtype)      # stands for the attention output
+
+    def step():
+        for layer in layers:
+            layer.qkv.matmul(h)
+            layer.o.matmul(a, out=layer._part[:M])
+            layer.mlp.forward(h, out=layer._part2[:M])
+
+    from ternaryllm_b200 import _lib
+
+    L = _lib.lib()
+    n0 = L.tllm_launch_count()
+    step()
+    torch.cuda.synchronize()
+    launches = (L.tllm_launch_count() - n0) // len(layers)
+    g = capture(torch, step)
+    us, _ = timed_us(torch, g.replay, 0.1)
+    return us / (launches * len(layers)), int(launches)
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -629,6 +660,15 @@ def main():
                                 "algorithmic_bytes_per_launch": h["algorithmic_bytes"], "physical_bytes_per_launch": h["physical_bytes"],
                                 "traffic": NCU_TRAFFIC["bytes"], "traffic_source": NCU_TRAFFIC["source"]}
             line["spmv"] = spmv
+        po = headline.get("products_only")
+        if po:
+            line["roofline_decoder"] = {"bound": "hbm", "achieved": po["algorithmic_GBps"], "peak": peak, "unit": "GB/s", "frac": po["algorithmic_GBps"] / peak,
+                                        "kernel": po["kernel"], "us_per_launch": po["us_per_launch"],
+                                        "workload": f"the {po['launches_per_layer']} ternary products of one decoder layer per rank (QKV, O, gate|up, down), "
+                                                    "mean over launches, weights streamed from HBM",
+                                        "algorithmic_bytes_per_launch": po["algorithmic_bytes_per_launch"],
+                                        "note": "the dominant kernel of the timed decoder step (about three quarters of its GPU time); algorithmic bytes = "
+                                                "the reference layout's 2 B per non-zero + 16 B per (column, 512 rows)"}
         if world == 1 and not a.no_cpu_baseline:
             try:
                 tps, desc = cpu_decoder_sample(budget_s=25.0)
