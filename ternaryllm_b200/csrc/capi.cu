@@ -15,6 +15,7 @@
 #include "mma_kernel.cuh"
 #include "nibble_format.h"
 #include "nibble_kernel.cuh"
+#include "nibble_rows_kernel.cuh"
 #include "util.h"
 
 namespace tllm {
@@ -84,9 +85,21 @@ static double gather_model_us(int64_t nnz, int rows) {
     const int idx = tail <= 1 ? 0 : (tail == 2 ? 1 : 2);
     return full * (GATHER_FIXED_US + nnz * GATHER_PS_PER_NNZ[2] * 1e-6) + (tail ? GATHER_FIXED_US + nnz * GATHER_PS_PER_NNZ[idx] * 1e-6 : 0.0);
 }
+// more rows than one such launch takes: the pieces kernel + the many-row kernel, up to 64 (32 fp32) rows per launch.
+// Measured per launch with 32 / 64 / 128 / 256 piece rows: start-up and hand-over grow with the rows, and the stream
+// slows down as the B tiles it re-reads from L2 and the MMAs grow with the piece rows.
+static const double NR_FIXED_US[4] = {13.5, 19.2, 26.9, 42.6}, NR_US_PER_MENTRY[4] = {0.081, 0.075, 0.090, 0.158};
 static double nibble_model_us(int64_t entries, int rows, int rows_per_launch) {
-    const int launches = (rows + rows_per_launch - 1) / rows_per_launch;
-    return launches * (NB_FIXED_US + entries * NB_US_PER_ENTRY) + (rows - launches) * NB_ROW_US;
+    if (rows <= rows_per_launch) return NB_FIXED_US + entries * NB_US_PER_ENTRY + (rows - 1) * NB_ROW_US;
+    const int per2 = rows_per_launch * (NR_MAX_NB / NB_ROWS), pieces = NB_ROWS / rows_per_launch;
+    double t = 0;
+    for (int r0 = 0; r0 < rows; r0 += per2) {
+        const int m = rows - r0 < per2 ? rows - r0 : per2;
+        int i = 0;
+        while ((32 << i) < m * pieces) ++i;
+        t += NR_FIXED_US[i] + entries * 1e-6 * NR_US_PER_MENTRY[i];
+    }
+    return t;
 }
 static double mm_model_us(int64_t entries, int rows) { return 9.8 + entries * 0.205e-6 * (rows <= 64 ? 1.0 : rows / 64.0); }
 static bool mm_model_prefers_tensor(int64_t nnz, int64_t entries, int rows) {
@@ -133,6 +146,13 @@ struct tllm_weight {
     float* d_nb_partial = nullptr;
     unsigned int* d_nb_counters = nullptr;
     uint32_t* d_nb_sched = nullptr;
+    // many-row variant: the activation pieces of a call, their tensor maps (32 / 64 / 128 / 256 piece rows), scratch
+    uint8_t* d_nr_pieces = nullptr;
+    float* d_nr_row_pow = nullptr;
+    float* d_nr_partial = nullptr;
+    unsigned int* d_nr_counters = nullptr;
+    CUtensorMap nr_map[4];
+    int nb_k_pad = 0, nr_grid = 0;
     // the activation tensor map of the last tensor-core launch (encoding one costs more than a short launch)
     CUtensorMap tmap;
     const void* tmap_x = nullptr;
@@ -382,13 +402,99 @@ int upload_nibbles(tllm_weight* w, const int8_t* dense, int inners, int columns,
     CU_TRY(cudaMalloc(&w->d_nb_counters, counter_bytes));
     CU_TRY(cudaMemset(w->d_nb_counters, 0, counter_bytes));
     w->scratch_bytes += partial_bytes + counter_bytes;
+    // the many-row variant: pieces of up to NR_MAX_NB piece rows, one tensor map per B height, two hand-over slots per block
+    w->nb_k_pad = img.k_pad;
+    w->nr_grid = sms;
+    const size_t pieces_bytes = (size_t)NR_MAX_NB * img.k_pad, nr_partial_bytes = (size_t)2 * sms * NB_TILE_N * NR_MAX_ROWS * sizeof(float);
+    CU_TRY(cudaMalloc(&w->d_nr_pieces, pieces_bytes));
+    CU_TRY(cudaMemset(w->d_nr_pieces, 0, pieces_bytes));
+    CU_TRY(cudaMalloc(&w->d_nr_row_pow, NR_MAX_ROWS * sizeof(float)));
+    CU_TRY(cudaMalloc(&w->d_nr_partial, nr_partial_bytes));
+    CU_TRY(cudaMalloc(&w->d_nr_counters, counter_bytes));
+    CU_TRY(cudaMemset(w->d_nr_counters, 0, counter_bytes));
+    w->scratch_bytes += pieces_bytes + nr_partial_bytes + counter_bytes;
+    for (int i = 0; i < 4; ++i) {
+        const cuuint64_t pdims[2] = {(cuuint64_t)img.k_pad, (cuuint64_t)NR_MAX_NB};
+        const cuuint64_t pstrides[1] = {(cuuint64_t)img.k_pad};
+        const cuuint32_t pbox[2] = {NB_TILE_K, (cuuint32_t)(32 << i)};
+        const CUresult pr = tensor_map_encoder()(&w->nr_map[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w->d_nr_pieces, pdims, pstrides, pbox, estr,
+                                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (pr != CUDA_SUCCESS) return fail(TLLM_ERR_CUDA, "cuTensorMapEncodeTiled (activation pieces) failed with code %d", (int)pr);
+    }
     CU_TRY(cudaDeviceSynchronize());
     return TLLM_OK;
 }
 
-// `rows` activation rows through the decode tensor-core kernel, a launch per group of rows that fits its B operand
+// more rows than one launch of nibble_spmm_kernel takes: the pieces kernel and the many-row kernel, up to NR_MAX_NB piece rows per pair
+int run_nr(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void* Y, int y_dtype, int y_ld, int epilogue, float scale, float scale2,
+           cudaStream_t st) {
+    const BsLayout& L = w->lay;
+    static std::mutex mu;
+    static bool configured[64] = {};
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (w->device < 64 && !configured[w->device]) {
+            CU_TRY(cudaFuncSetAttribute(nibble_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            configured[w->device] = true;
+        }
+    }
+    const int P = x_dtype == TLLM_F32 ? 8 : 4, per = NR_MAX_NB / P;
+    const size_t xe = dtype_size(x_dtype), ye = dtype_size(y_dtype);
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    for (int r0 = 0; r0 < rows; r0 += per) {
+        const int M = rows - r0 < per ? rows - r0 : per;
+        int mi = 0;
+        while ((32 << mi) < M * P) ++mi;
+        const int NB = 32 << mi;
+        NpParams q{};
+        q.X = (const char*)X + (size_t)r0 * x_ld * xe;
+        q.pieces = w->d_nr_pieces;
+        q.row_pow = w->d_nr_row_pow;
+        q.M = M, q.K = L.inners, q.k_pad = w->nb_k_pad, q.x_dtype = x_dtype, q.x_ld = x_ld, q.P = P;
+        cudaLaunchConfig_t c1{};
+        c1.gridDim = dim3((unsigned)M);
+        c1.blockDim = dim3(256);
+        c1.stream = st;
+        c1.attrs = at;
+        c1.numAttrs = 1;
+        CU_TRY(cudaLaunchKernelEx(&c1, nibble_pieces_kernel, q));
+        NrParams p{};
+        p.row_pow = w->d_nr_row_pow;
+        p.Y = (char*)Y + (size_t)r0 * y_ld * ye;
+        p.partial = w->d_nr_partial;
+        p.counters = w->d_nr_counters;
+        p.status = w->d_status;
+        p.M = M, p.N = L.columns;
+        p.y_dtype = y_dtype, p.y_ld = y_ld, p.epilogue = epilogue;
+        p.P = P, p.NB = NB, p.KB = w->nb_kb, p.n_tiles = w->nb_tiles;
+        const size_t stage = (size_t)NR_UK * (NB_A_STAGE_BYTES + (size_t)NB * 128);
+        p.S = (int)std::min<size_t>(NB_MAX_STAGES, (200 * 1024) / stage);
+        p.idesc = (1u << 4) | (5u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(NB_TILE_N >> 4) << 24);
+        p.tmem_cols = (uint32_t)(2 * NB);
+        p.scale = scale, p.scale2 = scale2;
+        const long long units = (long long)p.n_tiles * ((p.KB + NR_UK - 1) / NR_UK);
+        cudaLaunchConfig_t c2{};
+        c2.gridDim = dim3((unsigned)(units < w->nr_grid ? units : w->nr_grid));
+        c2.blockDim = dim3(NR_THREADS);
+        c2.dynamicSmemBytes = 1024 + (size_t)p.S * stage + 1024;
+        c2.stream = st;
+        c2.attrs = at;
+        c2.numAttrs = 1;
+        CU_TRY(cudaLaunchKernelEx(&c2, nibble_rows_kernel, w->nib_map, w->nr_map[mi], p));
+        g_launches.fetch_add(2, std::memory_order_relaxed);
+        g_nb_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    return TLLM_OK;
+}
+
+// `rows` activation rows through the decode tensor-core kernel: one launch for up to four rows (two for fp32), the many-row
+// pair of kernels above that
 int run_nb(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void* Y, int y_dtype, int y_ld, int epilogue, float scale, float scale2,
            cudaStream_t st) {
+    if (rows > nb_rows_per_launch(x_dtype)) return run_nr(w, X, x_dtype, x_ld, rows, Y, y_dtype, y_ld, epilogue, scale, scale2, st);
     const BsLayout& L = w->lay;
     static std::mutex mu;
     static bool configured[64] = {};
@@ -859,6 +965,10 @@ int tllm_weight_destroy(tllm_weight* w) {
     cudaFree(w->d_nb_partial);
     cudaFree(w->d_nb_counters);
     cudaFree(w->d_nb_sched);
+    cudaFree(w->d_nr_pieces);
+    cudaFree(w->d_nr_row_pow);
+    cudaFree(w->d_nr_partial);
+    cudaFree(w->d_nr_counters);
     cudaFree(w->d_partial);
     cudaFree(w->d_counters);
     cudaFree(w->d_status);
@@ -997,6 +1107,7 @@ int tllm_weight_check(tllm_weight* w) {
         cudaMemset(w->d_counters, 0, (size_t)w->lay.col_blocks * sizeof(unsigned int));
         if (w->d_mm_counters) cudaMemset(w->d_mm_counters, 0, (size_t)w->mm_n_tiles * 4 * sizeof(unsigned int));
         if (w->d_nb_counters) cudaMemset(w->d_nb_counters, 0, (size_t)w->nb_tiles * 4 * sizeof(unsigned int));
+        if (w->d_nr_counters) cudaMemset(w->d_nr_counters, 0, (size_t)w->nb_tiles * 4 * sizeof(unsigned int));
         return fail(TLLM_ERR_KERNEL, "a bounded wait ran out inside the kernel (code %d: %s)", st,
                     st == MM_ERR_WAIT ? "tensor-core pipeline stalled" : (st == NB_ERR_WAIT ? "decode tensor-core pipeline stalled" : "block table never arrived"));
     }

@@ -28,7 +28,7 @@ def dev():
 def nibble_kernel_for_every_small_call():
     """Pins the choice, so that which kernel runs does not depend on the cost model (tested on its own below)."""
     L = _lib.lib()
-    prev = L.tllm_set_nibble_max_rows(64)
+    prev = L.tllm_set_nibble_max_rows(128)
     yield
     L.tllm_set_nibble_max_rows(prev)
 
@@ -37,8 +37,10 @@ def launches():
     return _lib.lib().tllm_nibble_launch_count()
 
 
-def per_launch(dtype):
-    return 2 if dtype == "f32" else 4
+def expected_launches(M, dtype):
+    """up to four rows (two for fp32): one launch of the small kernel; above that the many-row kernel, 64 (32) rows per launch"""
+    small, big = (2, 32) if dtype == "f32" else (4, 64)
+    return 1 if M <= small else -(-M // big)
 
 
 # K not a multiple of 128, N not a multiple of 128, one and several K ranges (4096 rows each), one K block
@@ -54,7 +56,7 @@ def test_exact_on_integer_activations(K, N, s, dtype):
     pw = PackedWeight.from_dense(w, scale=1.0)
     assert pw.info["nibble_bytes"] == ((N + 127) // 128 * 128) * ((K + 127) // 128 * 128) // 2
     top = {"f16": 512, "bf16": 127, "f32": 100000}[dtype]          # exactly representable magnitudes of each type
-    for M in (1, 2, 3, 4, 5, 9):
+    for M in (1, 2, 3, 4, 5, 9, 16, 33, 64, 70):
         xs = rng.integers(-top, top + 1, size=(M, K)).astype(np.float64)
         if dtype == "f32" and K * top * 4 > 2 ** 24:
             xs = np.round(xs / 64)                                  # keep every partial sum below 2^24
@@ -62,7 +64,7 @@ def test_exact_on_integer_activations(K, N, s, dtype):
         Y = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev())
         n0 = launches()
         pw.matmul(X, out=Y)
-        assert launches() == n0 + -(-M // per_launch(dtype)), "the call did not run on the decode tensor-core kernel"
+        assert launches() == n0 + expected_launches(M, dtype), "the call did not run on the decode tensor-core kernel"
         want = oracle.dense_f64(xs, w, 1.0)
         assert np.array_equal(Y.double().cpu().numpy(), want), (K, N, M)
     pw.check()
@@ -77,7 +79,7 @@ def test_tolerance_on_gaussian_activations_and_agreement_with_the_gather_kernel(
     s = float(np.float16(0.0371))
     pw = PackedWeight.from_dense(w, scale=s)
     L = _lib.lib()
-    for M in (1, 2, 4, 7):
+    for M in (1, 2, 4, 7, 16, 40, 64):
         X = torch.tensor(rng.standard_normal((M, K)), dtype=DT[dtype], device=dev())
         ref = oracle.dense_f64(X.double().cpu().numpy(), w, s)
         n0 = launches()
@@ -126,7 +128,7 @@ def test_wide_range_of_magnitudes_in_one_row():
 
 
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
-@pytest.mark.parametrize("M", [1, 3, 6])
+@pytest.mark.parametrize("M", [1, 3, 6, 16, 64])
 def test_fused_mlp_block_on_the_decode_tensor_core_kernel(dtype, M):
     rng = np.random.default_rng(3)
     hidden, inter = 1024, 2816
@@ -136,7 +138,7 @@ def test_fused_mlp_block_on_the_decode_tensor_core_kernel(dtype, M):
     X = torch.tensor(rng.standard_normal((M, hidden)), dtype=DT[dtype], device=dev())
     n0 = launches()
     Y = mlp.forward(X)
-    assert launches() == n0 + 2 * -(-M // 4), "gate/up and down did not both run on the decode tensor-core kernel"
+    assert launches() == n0 + 2, "gate/up and down did not both run on the decode tensor-core kernel"
     ref = oracle.mlp_f64(X.double().cpu().numpy(), wg, wu, wd, sg, su, sd, h_round={"f16": 1, "bf16": 2}[dtype])
     err = np.max(np.abs(Y.double().cpu().numpy() - ref)) / np.max(np.abs(ref))
     assert err <= TOL + {"f16": 2.0 ** -10, "bf16": 2.0 ** -7}[dtype], err
