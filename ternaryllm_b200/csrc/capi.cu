@@ -563,10 +563,10 @@ int run_nb(tllm_weight* w, const void* X, int x_dtype, int x_ld, int rows, void*
 enum KernelChoice { KERNEL_GATHER, KERNEL_MMA, KERNEL_NIBBLE };
 KernelChoice choose_kernel(const tllm_weight* w, const void* X, int x_dtype, int x_layout, int x_ld, int rows) {
     const bool nb = nb_usable(w, x_dtype, x_layout, rows), mm = mm_usable(w, X, x_dtype, x_layout, x_ld, rows);
+    if (nb && g_nb_max_rows.load(std::memory_order_relaxed) > 0) return KERNEL_NIBBLE;     // pinned
+    if (mm && mm_min_rows() > 0) return KERNEL_MMA;                                         // pinned
     if (nb && mm) {
         const int64_t entries = (int64_t)w->lay.inners * w->lay.columns;
-        const int forced = g_nb_max_rows.load(std::memory_order_relaxed);
-        if (forced > 0) return KERNEL_NIBBLE;
         return mm_model_us(entries, rows) < nibble_model_us(entries, rows, nb_rows_per_launch(x_dtype)) ? KERNEL_MMA : KERNEL_NIBBLE;
     }
     return nb ? KERNEL_NIBBLE : (mm ? KERNEL_MMA : KERNEL_GATHER);
