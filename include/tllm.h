@@ -51,9 +51,10 @@ int64_t tllm_mma_launch_count(void);
  *   rows > 0  the tensor-core kernel from that many activation rows on
  * Process-wide; returns the previous setting.  The environment variable TLLM_MMA_MIN_ROWS sets the initial one. */
 int tllm_set_mma_min_rows(int rows);
-/* Which kernel takes a call of a few rows (fp16 / bf16: up to 4, fp32: up to 2 rows per launch; more rows take several
- * launches): the gather kernel on the index lists, or the decode tensor-core kernel that streams the four-bit copy of W
- * by TMA (half a byte per entry whatever the sparsity; the gather kernel's cost grows with the non-zeros).
+/* Which kernel takes a call of a few rows: the gather kernel on the index lists, or the decode tensor-core kernels that
+ * stream the four-bit copy of W by TMA (half a byte per entry whatever the sparsity; the gather kernel's cost grows with
+ * the non-zeros): one launch for up to 4 rows (fp32: 2), a pair of launches (activation pieces, then the product) for up
+ * to 64 rows (fp32: 32), several pairs above that.
  *   rows < 0  decide per call from a measured cost model of the two (default)
  *   rows = 0  never the decode tensor-core kernel
  *   rows > 0  always, for calls of up to that many rows

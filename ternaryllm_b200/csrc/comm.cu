@@ -30,13 +30,17 @@
 namespace tllm {
 
 #define COMM_MAX_WORLD 16
+#define COMM_MAX_SPLIT 8        // thread blocks that share one activation row
 #define COMM_ERR_PEER_WAIT 201
 
 struct CommParams {
     const float* partial;               // [rows][hidden] this rank's partial sums
     float* recv[COMM_MAX_WORLD];        // every rank's receive buffer [2][world][max_rows][hidden] (own one included)
-    uint32_t* flags[COMM_MAX_WORLD];    // every rank's flags [2][world][max_rows]
+    uint32_t* flags[COMM_MAX_WORLD];    // every rank's flags [2][world][max_rows][COMM_MAX_SPLIT]
     uint32_t* epoch;                    // [max_rows] all-reduces this row has been through (local)
+    float* ssq;                         // [2][max_rows][COMM_MAX_SPLIT] the slices' sums of squares (local)
+    unsigned int* arrive;               // [2][max_rows] blocks of the row that have stored theirs (local)
+    int split;                          // thread blocks per row
     void* x;
     const void* weight;
     void* h;
@@ -55,35 +59,46 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     return v;
 }
 
+// One activation row is handled by `split` thread blocks, each a contiguous slice of the hidden dimension: the push to
+// the peers then leaves from several SMs at once (a single SM's stores over NVLink were the slowest part with four or
+// more ranks), and every block waits only for its own slice of the peers' rows.  The sum of squares of the row is put
+// together through global memory: every block stores its slice's part, arrives on a counter, waits (bounded) until all
+// blocks of the row have arrived and adds the parts in slice order -- all blocks, and all ranks, get the same bits.
+// The blocks of a row are at most COMM_MAX_SPLIT of one launch, far fewer than SMs, so they are resident together.
 template <typename T>
-__global__ void __launch_bounds__(1024) push_allreduce_add_rmsnorm_kernel(const __grid_constant__ CommParams p) {
+__global__ void __launch_bounds__(256) push_allreduce_add_rmsnorm_kernel(const __grid_constant__ CommParams p) {
     constexpr int NV = RmsVec<T>::N;   // values of T per 16 bytes
-    __shared__ float red[32];
-    const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
-    const int nvec4 = p.hidden / 4;
+    __shared__ float red[8];
+    __shared__ float total_s;
+    const int r = blockIdx.x / p.split, sl = blockIdx.x % p.split, tid = threadIdx.x, nt = blockDim.x;
+    const int slice = p.hidden / p.split;                  // values of this block's slice
+    const size_t off = (size_t)sl * slice;                 // first value of the slice inside the row
+    const int nvec4 = slice / 4, nvec = slice / NV;
     // The partial sums, the residual row and this row's epoch come from kernels earlier in the stream.
     pdl_wait();
     pdl_launch_dependents();
     const uint32_t e = p.epoch[r] + 1u;
     const size_t set = e & 1u;
-    const float4* mine = (const float4*)(p.partial + (size_t)r * p.hidden);
-    // ---- push this rank's row into its slot on every peer ----
+    if (sl == 0 && tid == 0) {                             // the other buffer set's barrier words are free again: clear them for call e + 1
+        p.arrive[(set ^ 1u) * p.max_rows + r] = 0u;
+    }
+    const float4* mine = (const float4*)(p.partial + (size_t)r * p.hidden + off);
+    // ---- push this rank's slice into its slot on every peer ----
     for (int q = 1; q < p.world; ++q) {
         const int peer = (p.rank + q) % p.world;   // start with the neighbour: ranks do not all hit the same GPU first
-        float4* dst = (float4*)(p.recv[peer] + ((set * p.world + p.rank) * p.max_rows + r) * (size_t)p.hidden);
+        float4* dst = (float4*)(p.recv[peer] + ((set * p.world + p.rank) * p.max_rows + r) * (size_t)p.hidden + off);
         for (int i = tid; i < nvec4; i += nt) dst[i] = __ldcg(mine + i);
     }
     __syncthreads();
     if (tid < p.world && tid != p.rank) {
         __threadfence_system();
-        st_release_sys(p.flags[tid] + (set * p.world + p.rank) * p.max_rows + r, e);
+        st_release_sys(p.flags[tid] + ((set * p.world + p.rank) * p.max_rows + r) * COMM_MAX_SPLIT + sl, e);
     }
     // ---- what does not depend on the peers is read while their rows are on the way: the residual row and the norm weight
-    T* x = (T*)p.x + (size_t)r * p.hidden;
-    T* h = (T*)p.h + (size_t)r * p.hidden;
-    const T* wgt = (const T*)p.weight;
-    constexpr int KEEP = 2;             // vectors of the row a thread keeps in registers
-    const int nvec = p.hidden / NV;
+    T* x = (T*)p.x + (size_t)r * p.hidden + off;
+    T* h = (T*)p.h + (size_t)r * p.hidden + off;
+    const T* wgt = p.weight ? (const T*)p.weight + off : nullptr;
+    constexpr int KEEP = 2;             // vectors of the slice a thread keeps in registers
     float keep[KEEP][8], gain[KEEP][8];
 #pragma unroll
     for (int k = 0; k < KEEP; ++k) {
@@ -93,9 +108,9 @@ __global__ void __launch_bounds__(1024) push_allreduce_add_rmsnorm_kernel(const 
             if (wgt) RmsVec<T>::load(wgt + (size_t)vi * NV, gain[k]);
         }
     }
-    // ---- wait for every peer's row ----
+    // ---- wait for this slice of every peer's row ----
     if (tid < p.world && tid != p.rank) {
-        const uint32_t* f = p.flags[p.rank] + (set * p.world + tid) * p.max_rows + r;
+        const uint32_t* f = p.flags[p.rank] + ((set * p.world + tid) * p.max_rows + r) * COMM_MAX_SPLIT + sl;
         if (ld_acquire_sys(f) != e) {
             const long long t0 = clock64();
             while (ld_acquire_sys(f) != e) {
@@ -107,8 +122,8 @@ __global__ void __launch_bounds__(1024) push_allreduce_add_rmsnorm_kernel(const 
         }
     }
     __syncthreads();
-    // ---- x += sum over ranks (rank order), h = x * rsqrt(mean(x^2) + eps) * weight ----
-    const float* mine_recv = p.recv[p.rank] + (set * p.world * p.max_rows + r) * (size_t)p.hidden;   // slot of rank 0, row r
+    // ---- x += sum over ranks (rank order) ----
+    const float* mine_recv = p.recv[p.rank] + (set * p.world * p.max_rows + r) * (size_t)p.hidden + off;   // slot of rank 0, row r, this slice
     const size_t slot_stride = (size_t)p.max_rows * p.hidden;
     float ss = 0.f;
     auto first_pass = [&](int vi, float (&v)[8]) {      // v holds the residual values on entry
@@ -143,9 +158,33 @@ __global__ void __launch_bounds__(1024) push_allreduce_add_rmsnorm_kernel(const 
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if ((tid & 31) == 0) red[tid >> 5] = ss;
     __syncthreads();
-    float tot = 0.f;
-    for (int w = 0; w < (nt + 31) / 32; ++w) tot += red[w];
-    const float inv = rsqrtf(tot / (float)p.hidden + p.eps);
+    // ---- the row's sum of squares: this slice's part out, all slices' parts in (slice order) ----
+    if (tid == 0) {
+        float part = 0.f;
+        for (int w = 0; w < (nt + 31) / 32; ++w) part += red[w];
+        float tot = part;
+        if (p.split > 1) {
+            float* parts = p.ssq + (set * p.max_rows + r) * COMM_MAX_SPLIT;
+            unsigned int* arr = p.arrive + set * p.max_rows + r;
+            __stcg(parts + sl, part);
+            __threadfence();
+            atomicAdd(arr, 1u);
+            const long long t0 = clock64();
+            while (*(volatile unsigned int*)arr < (unsigned int)p.split) {
+                if (clock64() - t0 > p.wait_clocks) {   // a block of this row never came: report, use what is there
+                    atomicExch(p.status, COMM_ERR_PEER_WAIT);
+                    break;
+                }
+            }
+            __threadfence();
+            tot = 0.f;
+            for (int i = 0; i < p.split; ++i) tot += __ldcg(parts + i);
+        }
+        total_s = tot;
+        if (sl == 0) p.epoch[r] = e;                       // every block of the row has read the epoch by now
+    }
+    __syncthreads();
+    const float inv = rsqrtf(total_s / (float)p.hidden + p.eps);
     auto second_pass = [&](int vi, float (&v)[8], const float* g) {
         if (g) {
 #pragma unroll
@@ -167,7 +206,6 @@ __global__ void __launch_bounds__(1024) push_allreduce_add_rmsnorm_kernel(const 
         if (wgt) RmsVec<T>::load(wgt + (size_t)vi * NV, g);
         second_pass(vi, v, wgt ? g : nullptr);
     }
-    if (tid == 0) p.epoch[r] = e;
 }
 
 }  // namespace tllm
@@ -179,6 +217,8 @@ struct tllm_comm {
     float* recv = nullptr;          // own receive buffer
     uint32_t* flags = nullptr;      // own flags
     uint32_t* epoch = nullptr;
+    float* ssq = nullptr;
+    unsigned int* arrive = nullptr;
     int* status = nullptr;
     float* peer_recv[COMM_MAX_WORLD] = {};
     uint32_t* peer_flags[COMM_MAX_WORLD] = {};
@@ -203,12 +243,15 @@ int tllm_comm_create(int world, int rank, int max_rows, int hidden, tllm_comm** 
     tllm_comm* c = new tllm_comm();
     c->world = world, c->rank = rank, c->max_rows = max_rows, c->hidden = hidden;
     c->recv_bytes = (size_t)2 * world * max_rows * hidden * sizeof(float);
-    c->flag_bytes = (size_t)2 * world * max_rows * sizeof(uint32_t);
+    c->flag_bytes = (size_t)2 * world * max_rows * COMM_MAX_SPLIT * sizeof(uint32_t);
     cudaError_t e = cudaGetDevice(&c->device);
     if (e == cudaSuccess) e = cudaMalloc(&c->recv, c->recv_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&c->flags, c->flag_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&c->epoch, (size_t)max_rows * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&c->status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&c->ssq, (size_t)2 * max_rows * COMM_MAX_SPLIT * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&c->arrive, (size_t)2 * max_rows * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(c->arrive, 0, (size_t)2 * max_rows * sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMemset(c->flags, 0, c->flag_bytes);
     if (e == cudaSuccess) e = cudaMemset(c->epoch, 0, (size_t)max_rows * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(c->status, 0, sizeof(int));
@@ -303,6 +346,8 @@ int tllm_comm_destroy(tllm_comm* c) {
     cudaFree(c->recv);
     cudaFree(c->flags);
     cudaFree(c->epoch);
+    cudaFree(c->ssq);
+    cudaFree(c->arrive);
     cudaFree(c->status);
     delete c;
     return TLLM_OK;
@@ -325,16 +370,22 @@ int tllm_allreduce_add_rmsnorm(tllm_comm* c, const float* partial, void* x, cons
         p.flags[r] = c->peer_flags[r];
     }
     p.epoch = c->epoch;
+    p.ssq = c->ssq;
+    p.arrive = c->arrive;
     p.x = x, p.weight = weight, p.h = h;
     p.status = c->status;
     p.wait_clocks = c->wait_clocks;
     p.world = c->world, p.rank = c->rank, p.max_rows = c->max_rows, p.hidden = c->hidden;
     p.eps = eps;
     const int vec = dtype == TLLM_F32 ? 4 : 8;
-    int threads = (c->hidden / vec + 1) / 2;          // two vectors per thread stay in registers
-    threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : (threads + 31) / 32 * 32);
+    // slices of at least 1024 values, a whole number of 16-byte vectors each, at most COMM_MAX_SPLIT of them
+    int split = 1;
+    while (split < COMM_MAX_SPLIT && c->hidden % (split * 2 * 8) == 0 && c->hidden / (split * 2) >= 1024) split *= 2;
+    p.split = split;
+    int threads = (c->hidden / split / vec + 1) / 2;  // two vectors per thread stay in registers
+    threads = threads < 64 ? 64 : (threads > 256 ? 256 : (threads + 31) / 32 * 32);
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)rows);
+    cfg.gridDim = dim3((unsigned)(rows * split));
     cfg.blockDim = dim3((unsigned)threads);
     cfg.stream = (cudaStream_t)stream;
     cudaLaunchAttribute at[1];

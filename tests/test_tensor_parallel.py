@@ -150,8 +150,9 @@ def _comm(world, rank, rows, hidden):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("hidden,slices", [(1024, 1), (8192, 8)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-def test_peer_allreduce_with_a_stand_in_peer(dtype):
+def test_peer_allreduce_with_a_stand_in_peer(dtype, hidden, slices):
     """Rank 0 of a two-rank communicator on one GPU.  The peer is a pair of buffers of this process: the kernel pushes
     rank 0's rows into them (checked), and finds rank 1's rows and flag already in its own receive buffer, where the
     host put them -- the data path of a real peer without a second kernel that this one would have to wait for.
@@ -163,11 +164,11 @@ def test_peer_allreduce_with_a_stand_in_peer(dtype):
 
     L = _lib.lib()
     dev = torch.device("cuda", 0)
-    rows, hidden, world = 3, 1024, 2
+    rows, world = 3, 2           # a row of 8192 values is shared by eight thread blocks, one of 1024 by one
     h = _comm(world, 0, rows, hidden)
     recv, flags, rb, fb = C.c_void_p(), C.c_void_p(), C.c_int64(), C.c_int64()
     _lib.check(L.tllm_comm_buffers(h, C.byref(recv), C.byref(flags), C.byref(rb), C.byref(fb)))
-    assert rb.value == 2 * world * rows * hidden * 4 and fb.value == 2 * world * rows * 4
+    assert rb.value == 2 * world * rows * hidden * 4 and fb.value == 2 * world * rows * 8 * 4      # a flag per (set, rank, row, slice)
     peer_recv = torch.zeros(rb.value // 4, dtype=torch.float32, device=dev)
     peer_flags = torch.zeros(fb.value // 4, dtype=torch.int32, device=dev)
     _lib.check(L.tllm_comm_attach(h, 1, peer_recv.data_ptr(), peer_flags.data_ptr()))
@@ -180,7 +181,7 @@ def test_peer_allreduce_with_a_stand_in_peer(dtype):
         p1 = torch.randn((rows, hidden), generator=g).to(dev)
         # the peer's part: its rows into slot [set][source 1] of rank 0's receive buffer, then its flags
         _copy(recv.value + ((st * world + 1) * rows) * hidden * 4, p1.contiguous())
-        _copy(flags.value + ((st * world + 1) * rows) * 4, torch.full((rows,), epoch, dtype=torch.int32, device=dev))
+        _copy(flags.value + ((st * world + 1) * rows) * 8 * 4, torch.full((rows * 8,), epoch, dtype=torch.int32, device=dev))
         want_x = (x.float() + (p0 + p1)).to(dtype)
         hh = torch.empty_like(x)
         _lib.check(L.tllm_allreduce_add_rmsnorm(h, p0.data_ptr(), x.data_ptr(), wgt.data_ptr(), hh.data_ptr(), _lib.torch_dtype_code(dtype), rows,
@@ -194,7 +195,7 @@ def test_peer_allreduce_with_a_stand_in_peer(dtype):
         # what rank 0 pushed to its peer: its rows in slot [set][src = 0], and the flags
         got = peer_recv[((st * world + 0) * rows) * hidden:((st * world + 0) * rows + rows) * hidden].view(rows, hidden)
         assert torch.equal(got, p0)
-        assert torch.all(peer_flags[(st * world + 0) * rows:(st * world + 0) * rows + rows] == epoch)
+        assert torch.all(peer_flags[(st * world + 0) * rows * 8:((st * world + 0) * rows + rows) * 8].view(rows, 8)[:, :slices] == epoch)
     L.tllm_comm_destroy(h)
 
 
