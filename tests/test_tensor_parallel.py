@@ -150,39 +150,44 @@ def _comm(world, rank, rows, hidden):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("hidden,slices", [(1024, 1), (8192, 8)])
+@pytest.mark.parametrize("hidden,world,slices", [(1024, 2, 1), (8192, 2, 1), (8192, 4, 8)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-def test_peer_allreduce_with_a_stand_in_peer(dtype, hidden, slices):
-    """Rank 0 of a two-rank communicator on one GPU.  The peer is a pair of buffers of this process: the kernel pushes
-    rank 0's rows into them (checked), and finds rank 1's rows and flag already in its own receive buffer, where the
-    host put them -- the data path of a real peer without a second kernel that this one would have to wait for.
-    x += p0 + p1 in fp32, rounded once; h = RMSNorm(x) * weight.  Three calls in a row: the epochs and the two buffer
-    sets advance."""
+def test_peer_allreduce_with_a_stand_in_peer(dtype, hidden, world, slices):
+    """Rank 0 of a two- or four-rank communicator on one GPU.  The peers are one pair of buffers of this process: the
+    kernel pushes rank 0's rows into them (checked), and finds the other ranks' rows and flags already in its own receive
+    buffer, where the host put them -- the data path of real peers without a second kernel that this one would have to
+    wait for.  x += p0 + p1 (+ p2 + p3), in rank order, in fp32, rounded once; h = RMSNorm(x) * weight.  Three calls in a
+    row: the epochs and the two buffer sets advance.  From four ranks on, a row of 8192 values is shared by eight
+    thread blocks that meet at a barrier in global memory for the sum of squares."""
     import ctypes as C
 
     from ternaryllm_b200 import _lib
 
     L = _lib.lib()
     dev = torch.device("cuda", 0)
-    rows, world = 3, 2           # a row of 8192 values is shared by eight thread blocks, one of 1024 by one
+    rows = 3                     # from four ranks on a row of 8192 values is shared by eight thread blocks
     h = _comm(world, 0, rows, hidden)
     recv, flags, rb, fb = C.c_void_p(), C.c_void_p(), C.c_int64(), C.c_int64()
     _lib.check(L.tllm_comm_buffers(h, C.byref(recv), C.byref(flags), C.byref(rb), C.byref(fb)))
     assert rb.value == 2 * world * rows * hidden * 4 and fb.value == 2 * world * rows * 8 * 4      # a flag per (set, rank, row, slice)
     peer_recv = torch.zeros(rb.value // 4, dtype=torch.float32, device=dev)
     peer_flags = torch.zeros(fb.value // 4, dtype=torch.int32, device=dev)
-    _lib.check(L.tllm_comm_attach(h, 1, peer_recv.data_ptr(), peer_flags.data_ptr()))
+    for peer in range(1, world):
+        _lib.check(L.tllm_comm_attach(h, peer, peer_recv.data_ptr(), peer_flags.data_ptr()))
     g = torch.Generator(device="cpu").manual_seed(1)
     x = torch.randn((rows, hidden), generator=g).to(dev, dtype)
     wgt = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dev, dtype)
     for call in range(3):
         epoch, st = call + 1, (call + 1) & 1
         p0 = torch.randn((rows, hidden), generator=g).to(dev)
-        p1 = torch.randn((rows, hidden), generator=g).to(dev)
-        # the peer's part: its rows into slot [set][source 1] of rank 0's receive buffer, then its flags
-        _copy(recv.value + ((st * world + 1) * rows) * hidden * 4, p1.contiguous())
-        _copy(flags.value + ((st * world + 1) * rows) * 8 * 4, torch.full((rows * 8,), epoch, dtype=torch.int32, device=dev))
-        want_x = (x.float() + (p0 + p1)).to(dtype)
+        total = p0.clone()
+        for src in range(1, world):
+            # a peer's part: its rows into slot [set][source] of rank 0's receive buffer, then its flags (one per slice)
+            pk = torch.randn((rows, hidden), generator=g).to(dev)
+            _copy(recv.value + ((st * world + src) * rows) * hidden * 4, pk.contiguous())
+            _copy(flags.value + ((st * world + src) * rows) * 8 * 4, torch.full((rows * 8,), epoch, dtype=torch.int32, device=dev))
+            total = total + pk
+        want_x = (x.float() + total).to(dtype)
         hh = torch.empty_like(x)
         _lib.check(L.tllm_allreduce_add_rmsnorm(h, p0.data_ptr(), x.data_ptr(), wgt.data_ptr(), hh.data_ptr(), _lib.torch_dtype_code(dtype), rows,
                                                 1e-6, torch.cuda.current_stream().cuda_stream))
