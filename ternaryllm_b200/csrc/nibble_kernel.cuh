@@ -524,10 +524,13 @@ __global__ void __launch_bounds__(NB_THREADS, UK == 1 ? 2 : 1) nibble_spmm_kerne
         int tile = u0 / KUj, ku0 = u0 - tile * KUj;
         for (int u = u0; u < u1;) {
             const int ku1 = min(KUj, ku0 + (u1 - u));
+            const bool full = p.k_splits == 1 && ku0 == 0 && ku1 == KUj;
+            // read before the wait, so that the latency hides behind the MMAs: how many blocks hold a part of this tile,
+            // and (lane jj) the run of blocks of K range jj that do
+            const uint32_t parts = full ? 1u : __ldg(p.sched + tile);
+            const uint32_t my_run = (!full && lane < p.k_splits) ? __ldg(p.sched + (size_t)(1 + lane) * p.n_tiles + tile) : 1u;   // 1: an empty run
             NB_WAIT_BLOCK(ACC_FULL(a), aph);
             tc_fence_after();
-            const bool full = p.k_splits == 1 && ku0 == 0 && ku1 == KUj;
-            const uint32_t parts = full ? 1u : __ldg(p.sched + tile);     // read before the wait: the latency hides behind the MMAs
             const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + a * NB_ROWS;
             const int n = tile * NB_TILE_N + nl;
             auto emit = [&](float v, int m) {      // called by all lanes of the warp with the same m
@@ -566,15 +569,48 @@ __global__ void __launch_bounds__(NB_THREADS, UK == 1 ? 2 : 1) nibble_spmm_kerne
                 last = __shfl_sync(0xffffffffu, last, 0);
                 if (last) {
                     __threadfence();
-                    for (int m = 0; m < p.M; ++m) {
-                        float acc = 0.f;
-                        for (int jj = 0; jj < p.k_splits; ++jj) {
-                            const uint32_t fl = __ldg(p.sched + (size_t)(1 + jj) * p.n_tiles + tile);
-                            for (uint32_t c2 = fl & 0xFFFFu; c2 <= (fl >> 16); ++c2)
-                                acc += __ldcg(p.partial + ((size_t)(jj * slots_per_split + tile + c2) * (size_t)p.M + m) * NB_TILE_N + nl);
+                    // The parts of a tile: for every K range a run of slots (first and last block of the range that
+                    // hold some of the tile).  Lane jj keeps the run of range jj; the loads go out sixteen at a time --
+                    // one after the other they cost an L2 round trip each, and the block that adds a tile's parts is the
+                    // last one of the launch to finish.  The order of the additions stays: ranges, then blocks.
+                    constexpr int MAX_M = NB_ROWS / 4;     // rows of one launch: four pieces or more each
+                    float acc[MAX_M];
+#pragma unroll
+                    for (int m = 0; m < MAX_M; ++m) acc[m] = 0.f;
+                    int jj = 0;
+                    uint32_t run = __shfl_sync(0xffffffffu, my_run, 0);
+                    uint32_t c2 = run & 0xFFFFu, hi = run >> 16;
+                    for (;;) {
+                        float v[16][MAX_M];
+                        int got = 0;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            while (jj < p.k_splits && c2 > hi) {
+                                if (++jj < p.k_splits) {
+                                    run = __shfl_sync(0xffffffffu, my_run, jj & 31);
+                                    if (jj >= 32) run = __ldg(p.sched + (size_t)(1 + jj) * p.n_tiles + tile);
+                                    c2 = run & 0xFFFFu, hi = run >> 16;
+                                }
+                            }
+                            if (jj < p.k_splits) {
+                                const float* part = p.partial + ((size_t)(jj * slots_per_split + tile + c2) * (size_t)p.M) * NB_TILE_N + nl;
+#pragma unroll
+                                for (int m = 0; m < MAX_M; ++m) v[i][m] = m < p.M ? __ldcg(part + (size_t)m * NB_TILE_N) : 0.f;
+                                ++c2;
+                                got = i + 1;
+                            }
                         }
-                        emit(acc, m);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (i < got) {
+#pragma unroll
+                                for (int m = 0; m < MAX_M; ++m) acc[m] += v[i][m];
+                            }
+                        if (got < 16) break;
                     }
+#pragma unroll
+                    for (int m = 0; m < MAX_M; ++m)
+                        if (m < p.M) emit(acc[m], m);
                 }
             }
             a ^= 1u;
