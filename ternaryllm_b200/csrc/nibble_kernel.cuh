@@ -577,37 +577,38 @@ __global__ void __launch_bounds__(NB_THREADS, UK == 1 ? 2 : 1) nibble_spmm_kerne
                     float acc[MAX_M];
 #pragma unroll
                     for (int m = 0; m < MAX_M; ++m) acc[m] = 0.f;
-                    int jj = 0;
+                    int jj = 0, got;
                     uint32_t run = __shfl_sync(0xffffffffu, my_run, 0);
                     uint32_t c2 = run & 0xFFFFu, hi = run >> 16;
-                    for (;;) {
+                    // (both unrolled loops leave at the first slot that is not used: the instructions of the unused
+                    // ones cost this warp, which the whole launch waits for, about a microsecond)
+                    do {
                         float v[16][MAX_M];
-                        int got = 0;
+                        got = 0;
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            while (jj < p.k_splits && c2 > hi) {
-                                if (++jj < p.k_splits) {
-                                    run = __shfl_sync(0xffffffffu, my_run, jj & 31);
-                                    if (jj >= 32) run = __ldg(p.sched + (size_t)(1 + jj) * p.n_tiles + tile);
-                                    c2 = run & 0xFFFFu, hi = run >> 16;
-                                }
+                            while (c2 > hi && ++jj < p.k_splits) {       // on to the next range that has blocks on this tile
+                                run = jj < 32 ? __shfl_sync(0xffffffffu, my_run, jj) : __ldg(p.sched + (size_t)(1 + jj) * p.n_tiles + tile);
+                                c2 = run & 0xFFFFu, hi = run >> 16;
                             }
-                            if (jj < p.k_splits) {
-                                const float* part = p.partial + ((size_t)(jj * slots_per_split + tile + c2) * (size_t)p.M) * NB_TILE_N + nl;
+                            if (c2 > hi) break;                          // no range left
+                            const float* part = p.partial + ((size_t)(jj * slots_per_split + tile + c2) * (size_t)p.M) * NB_TILE_N + nl;
+                            v[i][0] = __ldcg(part);
 #pragma unroll
-                                for (int m = 0; m < MAX_M; ++m) v[i][m] = m < p.M ? __ldcg(part + (size_t)m * NB_TILE_N) : 0.f;
-                                ++c2;
-                                got = i + 1;
-                            }
+                            for (int m = 1; m < MAX_M; ++m)
+                                if (m < p.M) v[i][m] = __ldcg(part + (size_t)m * NB_TILE_N);
+                            ++c2;
+                            got = i + 1;
                         }
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            if (i < got) {
+                        for (int i = 0; i < 16; ++i) {
+                            if (i >= got) break;
+                            acc[0] += v[i][0];
 #pragma unroll
-                                for (int m = 0; m < MAX_M; ++m) acc[m] += v[i][m];
-                            }
-                        if (got < 16) break;
-                    }
+                            for (int m = 1; m < MAX_M; ++m)
+                                if (m < p.M) acc[m] += v[i][m];
+                        }
+                    } while (got == 16);
 #pragma unroll
                     for (int m = 0; m < MAX_M; ++m)
                         if (m < p.M) emit(acc[m], m);
