@@ -78,8 +78,8 @@ static int g_nb_debug_tx = 0;   // diagnostic builds only: bytes a weight tile's
 static int g_nb_debug_stages = 0, g_nb_debug_flags = 0;
 #endif
 // one launch of the decode tensor-core kernel: half a byte per entry at 5.2 TB/s around 6.7 us of start-up (building B
-// once the preceding kernel has finished) and hand-over between blocks, 2.2 us more for every further row
-static const double NB_FIXED_US = 6.7, NB_ROW_US = 2.2, NB_US_PER_ENTRY = 0.5 / 5.2e6;
+// once the preceding kernel has finished) and hand-over between blocks, 0.9 us more for every further row
+static const double NB_FIXED_US = 6.7, NB_ROW_US = 0.9, NB_US_PER_ENTRY = 0.5 / 5.2e6;
 static double gather_model_us(int64_t nnz, int rows) {
     const int full = rows / 4, tail = rows % 4;
     const int idx = tail <= 1 ? 0 : (tail == 2 ? 1 : 2);
