@@ -654,7 +654,7 @@ def main():
             line["roofline"] = {"bound": "hbm", "achieved": h["algorithmic_GBps"], "peak": peak, "unit": "GB/s", "frac": h["frac"],
                                 "frac_physical": h["frac_physical"], "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
                                 "kernel": "nibble_spmm_kernel" if h["kernel"].startswith("decode") else "bstream_spmm_kernel<float,1>",
-                                "kernel_choice": "the library's cost model (both kernels' times are under spmv.headline.by_kernel)",
+                                "kernel_choice": "the library's cost model (the times of the gather and the decode tensor-core kernel, each pinned, are under spmv.headline.by_kernel)",
                                 "us_per_launch": h["us_per_launch"],
                                 "workload": f"decode product x[1,{K_IN}] fp16, W[{K_IN},{N_OUT}] 75% zeros, {h['weights_in_rotation']} weights in rotation (larger than L2)",
                                 "algorithmic_bytes_per_launch": h["algorithmic_bytes"], "physical_bytes_per_launch": h["physical_bytes"],

@@ -45,8 +45,9 @@ int64_t tllm_mma_launch_count(void);
 /* Which kernel tllm_spmm / tllm_mlp_forward run for fp16 / bf16 row-major activations: the gather kernel on the
  * index lists, or the tensor-core kernel on the dense two-bit copy of W (the reference has one kernel for M = 1
  * and one for M > 1, ternaryLLM_GPU/csrc/ter_spmm_kernel.cuh:352-372, and no tensor-core path).
- *   rows < 0  decide per call (default): one row always gathers, 16 or more rows always take the tensor-core kernel,
- *             2..15 rows go by a measured cost model of the two kernels
+ *   rows < 0  decide per call (default) from a measured cost model: one row never takes this kernel; from two rows on
+ *             it is a candidate whenever the model finds it faster than the gather kernel, and the call then goes to
+ *             the faster of it and the decode tensor-core kernels (tllm_set_nibble_max_rows)
  *   rows = 0  never the tensor-core kernel
  *   rows > 0  the tensor-core kernel from that many activation rows on
  * Process-wide; returns the previous setting.  The environment variable TLLM_MMA_MIN_ROWS sets the initial one. */

@@ -1,5 +1,5 @@
 """TernaryLinear: the operator module of the reference (ternaryLLM_GPU/TernaryLLM/TernaryLinear.py:115-182),
-same constructor arguments and buffer names, running on the B200 tile-stream kernel.
+same constructor arguments and buffer names, running on the library's B200 kernels through a packed handle.
 
 What is kept: `in_features`, `out_features`, `sparsity`, `uniform`, `uniform_blk_size`, `padding`,
 `padding_size`, `bias`, `device`, `dtype`; the attribute `ternary_weight` (int32 [K, N] on the CPU); the
@@ -121,7 +121,7 @@ class TernaryLinear(nn.Module):
         self._packed: dict[int, PackedWeight] = {}
 
     def packed(self, device: torch.device) -> PackedWeight:
-        """The tile-stream copy of the weight on `device`, packed on first use."""
+        """The packed handle of the weight on `device`, made on first use."""
         idx = device.index if device.index is not None else torch.cuda.current_device()
         pw = self._packed.get(idx)
         if pw is None:
