@@ -199,6 +199,19 @@ int tllm_pack_roundtrip(const int8_t* w, int inners, int columns, const tllm_pac
  * runs the validator that tllm_weight_load runs before it uploads anything.  Returns its verdict. */
 int tllm_pack_corrupt_check(const int8_t* w, int inners, int columns, const tllm_pack_opts* opts, int num_sms,
                             int what, int64_t where, uint32_t value);
+/* Shared-segment rows: this library's own sparse-segment image of a ternary matrix, host memory only.  The reference
+ * names such an encoding but holds no definition of it (SSR/README.md cites a paper; the one consumer,
+ * ternaryLLM_GPU/csrc/ter_spmm_kernel.cuh:159-160, is commented out), so these two functions have no counterpart there.
+ * The 8 columns of a group share, per segment of 256 rows, one ascending list of the rows any of them uses (a byte
+ * each) and a 16-bit word of two-bit codes per listed row: 2 + 3n bytes per (group, segment).  It is a storage and
+ * interchange form for matrices of 90 % zeros and more; no kernel reads it -- decode, then tllm_weight_create_dense.
+ * tllm_ssr_encode: w int8 [inners][columns] row-major; image == NULL only reports the size in *bytes.
+ * tllm_ssr_decode: validates the whole image (sizes, offsets, ascending rows, code words) before w_out is trusted. */
+int tllm_ssr_encode(const int8_t* w, int inners, int columns, uint8_t* image, size_t capacity, size_t* bytes);
+int tllm_ssr_decode(const uint8_t* image, size_t bytes, int inners, int columns, int8_t* w_out);
+/* a handle from such an image: decoded and validated on the host, then packed like tllm_weight_create_dense */
+int tllm_weight_create_ssr(const uint8_t* image, size_t bytes, int inners, int columns, float scale,
+                           const tllm_pack_opts* opts, tllm_weight** out);
 int tllm_weight_destroy(tllm_weight* w);
 int tllm_weight_get_info(const tllm_weight* w, tllm_weight_info* info);
 /* Packed-weight files: everything a handle holds on the device (index stream, block tables, block descriptors, the

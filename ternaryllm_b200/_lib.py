@@ -50,6 +50,9 @@ SIGNATURES = {
     "tllm_ter_spmm_prepare": (_I, [_P, _P, _I, _I, _I]),
     "tllm_ter_spmm_forget": (_I, [_P, _P]),
     "tllm_ternarize": (_I, [_P, _I, _I, _F, _F, _P, _P]),
+    "tllm_ssr_encode": (_I, [_P, _I, _I, _P, C.c_size_t, _P]),
+    "tllm_ssr_decode": (_I, [_P, C.c_size_t, _I, _I, _P]),
+    "tllm_weight_create_ssr": (_I, [_P, C.c_size_t, _I, _I, _F, _P, _P]),
     "tllm_weight_save": (_I, [_P, C.c_char_p]),
     "tllm_weight_load": (_I, [C.c_char_p, _P]),
     "tllm_weight_create_dense": (_I, [_P, _I, _I, _F, _P, _P]),

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtllm.so")
-SOURCES = ["capi.cu", "comm.cu", "packer.cpp", "bstream_pack.cpp"]
+SOURCES = ["capi.cu", "comm.cu", "packer.cpp", "bstream_pack.cpp", "ssr_format.cpp"]
 DEPS = ["kernels.cuh", "mma_kernel.cuh", "bstream_kernel.cuh", "nibble_kernel.cuh", "nibble_rows_kernel.cuh", "nibble_format.h", "bstream_format.h", "bittile_format.h", "column_lists.h", "util.h", os.path.join("..", "..", "include", "tllm.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

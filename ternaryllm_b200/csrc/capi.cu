@@ -928,6 +928,14 @@ int tllm_weight_create_mcsc(const int32_t* row_idx, const int32_t* col_off, int 
     return create_from_dense(dense.data(), inners, columns, scale, opts, out);
 }
 
+int tllm_weight_create_ssr(const uint8_t* image, size_t bytes, int inners, int columns, float scale, const tllm_pack_opts* opts, tllm_weight** out) {
+    if (!image || inners <= 0 || columns <= 0) return fail(TLLM_ERR_ARG, "tllm_weight_create_ssr: bad argument");
+    std::vector<int8_t> dense((size_t)inners * (size_t)columns);
+    const int rc = tllm_ssr_decode(image, bytes, inners, columns, dense.data());      // validates the whole image first
+    if (rc != TLLM_OK) return rc;
+    return create_from_dense(dense.data(), inners, columns, scale, opts, out);
+}
+
 int tllm_weight_create_mcsc_device(const int16_t* row_idx, int64_t row_idx_len, const int32_t* col_off, int columns, int inners, int tile_k,
                                    float scale, const tllm_pack_opts* opts, tllm_weight** out) {
     if (!row_idx || !col_off || columns <= 0 || inners <= 0 || tile_k <= 0 || row_idx_len < 0)

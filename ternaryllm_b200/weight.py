@@ -40,6 +40,14 @@ class PackedWeight:
                            device, opts)
 
     @classmethod
+    def from_ssr(cls, image, inners, columns, scale=1.0, device=None, **opts):
+        """From the library's sparse-segment image (`ternaryllm_b200.ssr.encode`): validated and decoded on the host."""
+        img = np.ascontiguousarray(np.asarray(image), dtype=np.uint8)
+        return cls._create(lambda o, h: lib().tllm_weight_create_ssr(np_ptr(img), img.size, int(inners), int(columns), float(scale),
+                                                                     C.byref(o), C.byref(h)),
+                           device, opts)
+
+    @classmethod
     def from_mcsc(cls, row_idx, col_off, columns, inners, tile_k, scale=1.0, device=None, **opts):
         ri = np.ascontiguousarray(np.asarray(row_idx), dtype=np.int32)
         co = np.ascontiguousarray(np.asarray(col_off), dtype=np.int32)
