@@ -193,6 +193,11 @@ int tllm_weight_create_cpu_format(int kind, int group, int chunk, const int32_t*
  * and fills info. */
 int tllm_pack_roundtrip(const int8_t* w, int inners, int columns, const tllm_pack_opts* opts, int num_sms,
                         int8_t* w_out, tllm_weight_info* info);
+/* Diagnostic that needs no GPU: how the decode tensor-core kernel's grid shares a weight of this shape on num_sms SMs.
+ * dims[6] = {K blocks of 128 rows, column tiles of 128, K blocks per range, ranges, thread blocks per range, K blocks
+ * per unit}; words (NULL = dims only) = (1 + ranges) * tiles entries: words[t] = thread blocks that hold a part of column
+ * tile t, words[(1 + j) * tiles + t] = first | last << 16 block of range j on tile t.  No counterpart in the reference. */
+int tllm_nibble_schedule(int inners, int columns, int num_sms, int* dims, uint32_t* words, size_t capacity_words);
 /* Test hook that needs no GPU: packs w, overwrites one field of the packed image (what: 1 table word `where`, 2 stream
  * byte `where`, 3 tile_rows, 4 tiles, 5 col_blocks, 6 k_splits, 7 tiles_per_cta, 8..9 / 12..13 a block descriptor's
  * table words / first vector / table offset / vectors, 10 column range `where`, 11 inners; 0 = nothing) with `value` and

@@ -60,6 +60,7 @@ SIGNATURES = {
     "tllm_weight_create_mcsc_device": (_I, [_P, _L, _P, _I, _I, _I, _F, _P, _P]),
     "tllm_weight_create_cpu_format": (_I, [_I, _I, _I, _P, _P, _I, _L, _I, _I, _F, _P, _P]),
     "tllm_pack_roundtrip": (_I, [_P, _I, _I, _P, _I, _P, _P]),
+    "tllm_nibble_schedule": (_I, [_I, _I, _I, _P, _P, C.c_size_t]),
     "tllm_pack_corrupt_check": (_I, [_P, _I, _I, _P, _I, _I, _L, C.c_uint32]),
     "tllm_weight_destroy": (_I, [_P]),
     "tllm_weight_get_info": (_I, [_P, _P]),

@@ -369,33 +369,14 @@ int upload_nibbles(tllm_weight* w, const int8_t* dense, int inners, int columns,
     if (cr != CUDA_SUCCESS) return fail(TLLM_ERR_CUDA, "cuTensorMapEncodeTiled (four-bit weight planes) failed with code %d", (int)cr);
     // One block per SM, two tiles per unit, K ranges of up to 32 blocks.  (Two blocks per SM with one tile per unit and
     // ranges of 16 -- a block's start-up and hand-over overlapping the other's streaming -- measured 5 to 35 % slower.)
-    const int bpsm = 1, max_kbs = NB_MAX_KBS, NB_UK = 2;
-    w->nb_uk = NB_UK;
-    // K ranges of at most max_kbs blocks, all ranges the same number of thread blocks, never more blocks in a range
-    // than its shortest list of (tile, K block) units
-    w->nb_kb = img.k_pad / NB_TILE_K;
-    w->nb_tiles = img.n_pad / NB_TILE_N;
-    w->nb_splits = (w->nb_kb + max_kbs - 1) / max_kbs;
-    w->nb_kbs = (w->nb_kb + w->nb_splits - 1) / w->nb_splits;
-    w->nb_splits = (w->nb_kb + w->nb_kbs - 1) / w->nb_kbs;
-    const int last_ku = (w->nb_kb - (w->nb_splits - 1) * w->nb_kbs + NB_UK - 1) / NB_UK;
-    long long gj = (long long)sms * bpsm / w->nb_splits;
-    if (gj < 1) gj = 1;
-    if (gj > (long long)w->nb_tiles * last_ku) gj = (long long)w->nb_tiles * last_ku;
-    w->nb_gj = (int)gj;
+    static_assert(NB_FMT_TILE == NB_TILE_K && NB_FMT_TILE == NB_TILE_N && NB_FMT_MAX_KBS == NB_MAX_KBS && NB_FMT_UK == 2,
+                  "the host schedule and the kernel (launched as nibble_spmm_kernel<2>) disagree");
+    NbSchedule plan;
+    nb_make_schedule(img.k_pad, img.n_pad, sms, &plan);
+    w->nb_uk = plan.uk, w->nb_kb = plan.kb, w->nb_tiles = plan.tiles, w->nb_kbs = plan.kbs, w->nb_splits = plan.splits, w->nb_gj = plan.gj;
+    const std::vector<uint32_t>& sched = plan.words;
     const size_t partial_bytes = (size_t)w->nb_splits * ((size_t)w->nb_tiles + w->nb_gj) * (NB_ROWS / 4) * NB_TILE_N * sizeof(float);
     const size_t counter_bytes = (size_t)w->nb_tiles * 4 * sizeof(unsigned int);
-    // which blocks hold a part of which column tile: block c of a range owns units [tot * c / gj, tot * (c + 1) / gj)
-    std::vector<uint32_t> sched((size_t)(1 + w->nb_splits) * w->nb_tiles, 0u);
-    for (int jj = 0; jj < w->nb_splits; ++jj) {
-        const long long kbn = std::min(w->nb_kbs, w->nb_kb - jj * w->nb_kbs), kun = (kbn + NB_UK - 1) / NB_UK, tot = (long long)w->nb_tiles * kun;
-        for (int t = 0; t < w->nb_tiles; ++t) {
-            const long long fu = (long long)t * kun, lu = fu + kun - 1;
-            const long long cf = ((fu + 1) * gj + tot - 1) / tot - 1, cl = ((lu + 1) * gj + tot - 1) / tot - 1;
-            sched[(size_t)t] += (uint32_t)(cl - cf + 1);
-            sched[(size_t)(1 + jj) * w->nb_tiles + t] = (uint32_t)cf | ((uint32_t)cl << 16);
-        }
-    }
     CU_TRY(cudaMalloc(&w->d_nb_sched, sched.size() * sizeof(uint32_t)));
     CU_TRY(cudaMemcpy(w->d_nb_sched, sched.data(), sched.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
     CU_TRY(cudaMalloc(&w->d_nb_partial, partial_bytes));

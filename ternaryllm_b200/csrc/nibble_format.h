@@ -22,3 +22,20 @@ struct NbHostImage {
 void nb_pack_dense(const int8_t* w, int inners, int columns, NbHostImage* out);
 // inverse, for tests of the packer alone; returns false on a code that is none of the three
 bool nb_unpack_dense(const NbHostImage& img, int8_t* w);
+
+// How the grid of nibble_spmm_kernel shares the work.  The K blocks (128 rows of W each) are cut into `splits` ranges
+// of up to `kbs` blocks (a block of threads keeps the activation pieces of one range in shared memory); a unit is `uk`
+// consecutive K blocks of one column tile; the units of a range, tile-major, are dealt out in equal contiguous runs to
+// `gj` thread blocks (block c of a range owns units [total * c / gj, total * (c + 1) / gj)), never more blocks than the
+// shortest range has units.  A column tile whose units lie in several thread blocks is added up by the last of them
+// to arrive, which has to know who the others are:
+//   words[t]                    how many thread blocks (all ranges) hold a part of column tile t
+//   words[(1 + j) * tiles + t]  first | last << 16: the run of blocks of range j that hold a part of tile t
+#define NB_FMT_TILE 128
+#define NB_FMT_MAX_KBS 32
+#define NB_FMT_UK 2
+struct NbSchedule {
+    int kb = 0, tiles = 0, kbs = 0, splits = 0, gj = 0, uk = NB_FMT_UK;
+    std::vector<uint32_t> words;
+};
+void nb_make_schedule(int k_pad, int n_pad, int sms, NbSchedule* out);

@@ -548,3 +548,43 @@ bool nb_unpack_dense(const NbHostImage& img, int8_t* w) {
         }
     return true;
 }
+
+void nb_make_schedule(int k_pad, int n_pad, int sms, NbSchedule* out) {
+    NbSchedule& s = *out;
+    s.uk = NB_FMT_UK;
+    s.kb = k_pad / NB_FMT_TILE;
+    s.tiles = n_pad / NB_FMT_TILE;
+    // ranges of at most NB_FMT_MAX_KBS blocks, as even as they come
+    s.splits = (s.kb + NB_FMT_MAX_KBS - 1) / NB_FMT_MAX_KBS;
+    s.kbs = (s.kb + s.splits - 1) / s.splits;
+    s.splits = (s.kb + s.kbs - 1) / s.kbs;
+    // every range the same number of thread blocks, one thread block per SM in all, never more than the last (shortest) range has units
+    const int last_ku = (s.kb - (s.splits - 1) * s.kbs + s.uk - 1) / s.uk;
+    long long gj = (long long)sms / s.splits;
+    if (gj < 1) gj = 1;
+    if (gj > (long long)s.tiles * last_ku) gj = (long long)s.tiles * last_ku;
+    if (gj > 0xFFFF) gj = 0xFFFF;                            // a run's ends are 16-bit fields
+    s.gj = (int)gj;
+    s.words.assign((size_t)(1 + s.splits) * s.tiles, 0u);
+    for (int jj = 0; jj < s.splits; ++jj) {
+        const long long kbn = std::min(s.kbs, s.kb - jj * s.kbs), kun = (kbn + s.uk - 1) / s.uk, tot = (long long)s.tiles * kun;
+        for (int t = 0; t < s.tiles; ++t) {
+            // the block that owns unit u is the largest c with tot * c / gj <= u, that is ceil((u + 1) * gj / tot) - 1
+            const long long fu = (long long)t * kun, lu = fu + kun - 1;
+            const long long cf = ((fu + 1) * gj + tot - 1) / tot - 1, cl = ((lu + 1) * gj + tot - 1) / tot - 1;
+            s.words[(size_t)t] += (uint32_t)(cl - cf + 1);
+            s.words[(size_t)(1 + jj) * s.tiles + t] = (uint32_t)cf | ((uint32_t)cl << 16);
+        }
+    }
+}
+
+extern "C" int tllm_nibble_schedule(int inners, int columns, int num_sms, int* dims, uint32_t* words, size_t capacity_words) {
+    if (inners <= 0 || columns <= 0 || num_sms <= 0 || !dims) return tllm::fail(TLLM_ERR_ARG, "tllm_nibble_schedule: bad argument");
+    NbSchedule s;
+    nb_make_schedule((inners + NB_FMT_TILE - 1) / NB_FMT_TILE * NB_FMT_TILE, (columns + NB_FMT_TILE - 1) / NB_FMT_TILE * NB_FMT_TILE, num_sms, &s);
+    dims[0] = s.kb, dims[1] = s.tiles, dims[2] = s.kbs, dims[3] = s.splits, dims[4] = s.gj, dims[5] = s.uk;
+    if (!words) return TLLM_OK;
+    if (capacity_words < s.words.size()) return tllm::fail(TLLM_ERR_ARG, "tllm_nibble_schedule: %zu words needed, %zu given", s.words.size(), capacity_words);
+    std::memcpy(words, s.words.data(), s.words.size() * sizeof(uint32_t));
+    return TLLM_OK;
+}
