@@ -350,6 +350,7 @@ def decoder_bench(torch, dist, world, rank, device, steps, warmup, sparsities, b
         alg_local = float(np.mean([l.alg_bytes_local for l in layers])) * d["layers"]
         note(f"{S:.0%} zeros: {nsets} layer weight set(s) packed ({per_set / 1e6:.0f} MB per set and rank)")
 
+        barrier()     # packing takes a different time on every rank; the peer reduce waits for a peer about a second, not longer
         # ---- parity before timing: one layer on the N ranks against the dense fp32 layer on rank 0 ----
         g = torch.Generator(device="cpu").manual_seed(7)
         Mc = min(4, max(batches))
